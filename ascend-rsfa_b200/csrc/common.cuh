@@ -1,0 +1,36 @@
+// Types shared by the kernels and the C-ABI dispatcher.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace rsfa {
+
+// One attention problem as the kernels see it: raw pointers plus element strides.
+struct FwdParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse;  // may be null
+  int B, H, S, D;
+  int64_t q_stride[3];  // batch, head, row (the innermost stride is 1)
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+  int causal;
+  float sm_scale;
+  int bf16;
+  int* status;                 // device status word, never null
+  unsigned int* tile_counter;  // device work-queue counter (persistent kernel)
+  unsigned long long wait_limit_ns;
+};
+
+// Launchers implemented in the kernel translation units.  Each returns a cudaError_t
+// from the launch itself and bumps *launches by the number of kernels it started.
+cudaError_t launch_fwd_generic(const FwdParams& p, cudaStream_t stream, long long* launches);
+cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t stream,
+                               long long* launches);
+// True when the tcgen05 kernel is instantiated for this head dimension.
+bool tcgen05_supports(int S, int D, float sm_scale);
+
+}  // namespace rsfa

@@ -1,0 +1,593 @@
+// FlashAttention-2 forward for B200 (sm_100a): warp-specialised, persistent,
+// tcgen05 tensor cores with accumulators in tensor memory, operands staged by TMA.
+//
+// It replaces the reference's tiled kernels: _attn_fwd with _attn_fwd_inner and
+// _attn_fwd_inner_d64_nc (ascend_rsfa/flash_attention_forward.py:163-404) and the
+// two-launch causal split _run_causal_split / _attn_fwd_split_inner (:408-541).
+// Where the reference runs the unmasked prefix and the masked diagonal as two
+// launches that pass l, m and an fp16 copy of the accumulator through global
+// memory (:338-368), this kernel runs both tile kinds in one sweep — an unmasked
+// loop body for prefix tiles and a masked one for the tile that crosses the
+// diagonal (or the ragged end of the sequence) — with the state in registers and
+// the accumulator in tensor memory.
+//
+// One CTA owns kNT query tiles of 128 rows ("Q tiles") of one (batch, head) and
+// sweeps the keys in tiles of 128.  Roles:
+//   warps 0..3   softmax group 0: one thread per row of Q tile 0
+//   warps 4..7   softmax group 1: one thread per row of Q tile 1
+//   warp  8      TMA producer (one lane): Q tiles once per work item, K/V tiles
+//                through a ring of kStages shared-memory slots
+//   warp  9      MMA issuer (one lane) and owner of the TMEM allocation
+// Per key tile j and Q tile t:
+//   S_t = Q_t K_j^T          tcgen05.mma, both operands from shared memory
+//   softmax group t          tcgen05.ld S_t -> running max, exp2, row sum -> P_t
+//                            (16-bit) written back over S_t with tcgen05.st; when a
+//                            row's max grew by more than 2^8 the group rescales its
+//                            O_t rows in TMEM first (the reference's "rescale
+//                            skipping" with threshold 0, :466-487, generalised)
+//   O_t += P_t V_j           tcgen05.mma, A from TMEM, B = V_j as an MN-major operand
+// The two Q tiles alternate on the tensor pipe, so the MMAs of one overlap the
+// softmax of the other.  TMEM columns: S_0 [0,128)  S_1 [128,256)  O_0 [256,256+D)
+// O_1 [256+D, 256+2D).
+//
+// Work items (batch*head, 256-row block) are handed out through an atomic
+// counter; a CTA keeps fetching until the queue is empty.  Causal items are
+// ordered heaviest first inside each head; items of one head are adjacent so the
+// CTAs working on them share its K and V through L2.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace rsfa {
+namespace {
+
+constexpr int kTileM = 128;   // rows per Q tile (= TMEM lanes)
+constexpr int kTileN = 128;   // keys per K/V tile
+constexpr int kNT = 2;        // Q tiles per CTA
+constexpr int kNumThreads = 320;
+constexpr int kTmaWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kTmemCols = 512;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+// Wait-site tags (reported in the status word when a wait runs out).
+enum : int {
+  kTagQEmpty = 1, kTagKvEmpty, kTagQFull, kTagKvFull, kTagPFull, kTagSFull, kTagOFull, kTagSched
+};
+
+template <int D>
+struct Cfg {
+  static constexpr int kBoxes = D / 64;                       // 64-column TMA boxes per row
+  static constexpr int kQTileBytes = kTileM * D * 2;
+  static constexpr int kKvTileBytes = kTileN * D * 2;
+  static constexpr int kStages = (D == 128) ? 4 : 6;
+  static constexpr int kQBoxBytes = kTileM * 128;             // 128 rows x 128 B
+  static constexpr int kKvBoxBytes = kTileN * 128;
+  static constexpr int kNumBarriers = 2 * kNT + 2 * kStages + 3 * kNT + 4;
+  static constexpr int kSmemBytes = kNT * kQTileBytes + kStages * kKvTileBytes + 1024 /*align*/ +
+                                    kNumBarriers * 8 + 64;
+  __host__ __device__ static constexpr int kColS(int t) { return t * kTileN; }
+  __host__ __device__ static constexpr int kColO(int t) { return 2 * kTileN + t * D; }
+};
+
+struct TmaMaps {
+  CUtensorMap q, k, v;
+};
+
+struct SchedInfo {
+  int total_items;
+  int items_per_head;  // 256-row blocks per head
+};
+
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (kBf16) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  } else {
+    __half2 t = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Number of key tiles Q tile (row0 .. row0+127) has to visit.
+__device__ __forceinline__ int num_kv_tiles(int row0, int S, int causal) {
+  if (row0 >= S) return 0;
+  const int last_key = causal ? min(S, row0 + kTileM) : S;  // exclusive
+  return (last_key + kTileN - 1) / kTileN;
+}
+
+template <int D, bool kBf16>
+__global__ void __launch_bounds__(kNumThreads, 1)
+fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, const SchedInfo sched) {
+  using C = Cfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte-swizzled tiles need 1024-byte alignment.
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = smem_base;
+  const uint32_t sKV = sQ + kNT * C::kQTileBytes;
+  const uint32_t sBar = sKV + C::kStages * C::kKvTileBytes;
+  // barrier addresses
+  auto bar_q_full = [&](int t) { return sBar + 8u * t; };
+  auto bar_q_empty = [&](int t) { return sBar + 8u * (kNT + t); };
+  auto bar_kv_full = [&](int s) { return sBar + 8u * (2 * kNT + s); };
+  auto bar_kv_empty = [&](int s) { return sBar + 8u * (2 * kNT + C::kStages + s); };
+  auto bar_s_full = [&](int t) { return sBar + 8u * (2 * kNT + 2 * C::kStages + t); };
+  auto bar_p_full = [&](int t) { return sBar + 8u * (3 * kNT + 2 * C::kStages + t); };
+  auto bar_o_full = [&](int t) { return sBar + 8u * (4 * kNT + 2 * C::kStages + t); };
+  const uint32_t bar_sched_full0 = sBar + 8u * (5 * kNT + 2 * C::kStages);  // 2 slots
+  const uint32_t bar_sched_empty0 = bar_sched_full0 + 16u;                   // 2 slots
+  const uint32_t misc = sBar + 8u * C::kNumBarriers;
+  // misc words: [0] TMEM base, [1] abort flag, [2..3] scheduler ring
+  uint8_t* misc_ptr = smem_raw + (misc - smem_u32(smem_raw));
+  volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(misc_ptr);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc_ptr + 4);
+  volatile int* sched_ring = reinterpret_cast<volatile int*>(misc_ptr + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint64_t wait_ns = p.wait_limit_ns;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int t = 0; t < kNT; ++t) {
+      mbar_init(bar_q_full(t), 1);
+      mbar_init(bar_q_empty(t), 1);
+      mbar_init(bar_s_full(t), 1);
+      mbar_init(bar_p_full(t), kTileM);
+      mbar_init(bar_o_full(t), 1);
+    }
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(bar_kv_full(s), 1);
+      mbar_init(bar_kv_empty(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_sched_full0 + 8u * s, 1);
+      mbar_init(bar_sched_empty0 + 8u * s, 1 + kNT * 4);  // MMA lane + one lane per softmax warp
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == kTmaWarp && lane == 0) {
+    tma_prefetch_desc(&maps.q);
+    tma_prefetch_desc(&maps.k);
+    tma_prefetch_desc(&maps.v);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  const int S = p.S;
+  const int items_per_head = sched.items_per_head;
+  // work item -> (head, first row).  Causal: heaviest (last) row block first.
+  auto decode = [&](int item, int& bh, int& row0) {
+    bh = item / items_per_head;
+    int blk = item - bh * items_per_head;
+    if (p.causal) blk = items_per_head - 1 - blk;
+    row0 = blk * (kNT * kTileM);
+  };
+
+  if (warp == kTmaWarp) {
+    // ================================================================ producer
+    if (lane == 0) {
+      uint32_t kv_count = 0;   // K/V tiles loaded so far (ring position)
+      uint32_t item_count = 0; // work items started so far
+      bool ok = true;
+      while (ok) {
+        // fetch the next work item and publish it to the other roles
+        const int slot = item_count & 1;
+        ok = mbar_wait(bar_sched_empty0 + 8u * slot, ((item_count >> 1) & 1) ^ 1, abort_flag, wait_ns,
+                       kTagSched);
+        if (!ok) break;
+        const int item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
+        sched_ring[slot] = item;
+        __threadfence_block();
+        mbar_arrive(bar_sched_full0 + 8u * slot);
+        if (item >= sched.total_items) break;
+        int bh, row0;
+        decode(item, bh, row0);
+        const int b = bh / p.H, h = bh - b * p.H;
+        int nmax = 0;
+        for (int t = 0; t < kNT; ++t) nmax = max(nmax, num_kv_tiles(row0 + t * kTileM, S, p.causal));
+
+        auto load_q = [&](int t) -> bool {
+          if (!mbar_wait(bar_q_empty(t), (item_count & 1) ^ 1, abort_flag, wait_ns, kTagQEmpty)) return false;
+          mbar_arrive_expect_tx(bar_q_full(t), C::kQTileBytes);
+          for (int bx = 0; bx < C::kBoxes; ++bx)
+            tma_load_4d(sQ + t * C::kQTileBytes + bx * C::kQBoxBytes, &maps.q, bar_q_full(t), bx * 64,
+                        row0 + t * kTileM, h, b);
+          return true;
+        };
+        auto load_kv = [&](const CUtensorMap* map, int j) -> bool {
+          const uint32_t s = kv_count % C::kStages;
+          const uint32_t ph = (kv_count / C::kStages) & 1;
+          if (!mbar_wait(bar_kv_empty(s), ph ^ 1, abort_flag, wait_ns, kTagKvEmpty)) return false;
+          mbar_arrive_expect_tx(bar_kv_full(s), C::kKvTileBytes);
+          for (int bx = 0; bx < C::kBoxes; ++bx)
+            tma_load_4d(sKV + s * C::kKvTileBytes + bx * C::kKvBoxBytes, map, bar_kv_full(s), bx * 64,
+                        j * kTileN, h, b);
+          ++kv_count;
+          return true;
+        };
+        ok = load_q(0);
+        if (ok && nmax > 0) ok = load_kv(&maps.k, 0);
+        if (ok) ok = load_q(1);
+        if (ok && nmax > 0) ok = load_kv(&maps.v, 0);
+        for (int j = 1; ok && j < nmax; ++j) {
+          ok = load_kv(&maps.k, j);
+          if (ok) ok = load_kv(&maps.v, j);
+        }
+        ++item_count;
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ============================================================== MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_f16(kTileM, kTileN, kBf16, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_f16(kTileM, D, kBf16, false, true);
+      uint32_t kv_count = 0, item_count = 0;
+      uint32_t p_count[kNT] = {0, 0};
+      bool ok = true;
+      while (ok) {
+        const int slot = item_count & 1;
+        ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
+        if (!ok) break;
+        const int item = sched_ring[slot];
+        mbar_arrive(bar_sched_empty0 + 8u * slot);
+        if (item >= sched.total_items) break;
+        int bh, row0;
+        decode(item, bh, row0);
+        int n[kNT];
+        int nmax = 0;
+        for (int t = 0; t < kNT; ++t) {
+          n[t] = num_kv_tiles(row0 + t * kTileM, S, p.causal);
+          nmax = max(nmax, n[t]);
+        }
+        // S_t = Q_t K^T : both operands K-major, 64-column boxes, 8-row atoms of 1024 B
+        auto issue_qk = [&](int t, uint32_t kslot) {
+          const uint32_t qa = sQ + t * C::kQTileBytes;
+          const uint32_t ka = sKV + kslot * C::kKvTileBytes;
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off_q = (ks >> 2) * C::kQBoxBytes + (ks & 3) * 32;
+            const uint32_t off_k = (ks >> 2) * C::kKvBoxBytes + (ks & 3) * 32;
+            umma_ss(tmem_base + C::kColS(t), make_smem_desc_sw128(qa + off_q, 16, 1024),
+                    make_smem_desc_sw128(ka + off_k, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+          }
+        };
+        // O_t (+)= P_t V : A = P_t in TMEM (16 keys = 8 columns per step), B = V MN-major:
+        // 16 keys per step = two 8-row atoms (stride 1024 B), 64-column boxes kKvBoxBytes apart.
+        auto issue_pv = [&](int t, uint32_t vslot, bool accumulate) {
+          const uint32_t va = sKV + vslot * C::kKvTileBytes;
+#pragma unroll
+          for (int ks = 0; ks < kTileN / 16; ++ks) {
+            umma_ts(tmem_base + C::kColO(t), tmem_base + C::kColS(t) + ks * 8,
+                    make_smem_desc_sw128(va + ks * 2048, C::kKvBoxBytes, 1024), idesc_pv,
+                    (accumulate || ks > 0) ? 1u : 0u);
+          }
+        };
+        auto wait_kv = [&](uint32_t idx) -> bool {
+          return mbar_wait(bar_kv_full(idx % C::kStages), (idx / C::kStages) & 1, abort_flag, wait_ns,
+                           kTagKvFull);
+        };
+
+        for (int t = 0; ok && t < kNT; ++t)
+          ok = mbar_wait(bar_q_full(t), item_count & 1, abort_flag, wait_ns, kTagQFull);
+        if (!ok) break;
+        const uint32_t base = kv_count;  // K_j at base + 2j, V_j at base + 2j + 1
+        if (nmax > 0) {
+          ok = wait_kv(base);
+          if (!ok) break;
+          tc_fence_after_sync();
+          for (int t = 0; t < kNT; ++t) {
+            if (n[t] > 0) {
+              issue_qk(t, base % C::kStages);
+              umma_commit(bar_s_full(t));
+            }
+          }
+          umma_commit(bar_kv_empty(base % C::kStages));
+        }
+        for (int j = 0; ok && j < nmax; ++j) {
+          const uint32_t vidx = base + 2 * j + 1;
+          const uint32_t kidx = base + 2 * j + 2;
+          ok = wait_kv(vidx);
+          if (!ok) break;
+          bool k_ready = false;
+          for (int t = 0; ok && t < kNT; ++t) {
+            if (j < n[t]) {
+              ok = mbar_wait(bar_p_full(t), p_count[t] & 1, abort_flag, wait_ns, kTagPFull);
+              if (!ok) break;
+              ++p_count[t];
+              tc_fence_after_sync();
+              issue_pv(t, vidx % C::kStages, j > 0);
+              if (j == n[t] - 1) umma_commit(bar_o_full(t));
+            }
+            if (j + 1 < n[t]) {
+              if (!k_ready) {
+                ok = wait_kv(kidx);
+                if (!ok) break;
+                tc_fence_after_sync();
+                k_ready = true;
+              }
+              issue_qk(t, kidx % C::kStages);
+              umma_commit(bar_s_full(t));
+            }
+          }
+          if (!ok) break;
+          umma_commit(bar_kv_empty(vidx % C::kStages));
+          if (j + 1 < nmax) {
+            if (!k_ready) {  // tile loaded for a Q tile that did not need it: still consume it
+              ok = wait_kv(kidx);
+              if (!ok) break;
+            }
+            umma_commit(bar_kv_empty(kidx % C::kStages));
+          }
+        }
+        if (!ok) break;
+        for (int t = 0; t < kNT; ++t) umma_commit(bar_q_empty(t));
+        kv_count += 2 * nmax;
+        ++item_count;
+      }
+    }
+  } else {
+    // ========================================================== softmax groups
+    const int t = warp >> 2;                   // Q tile of this group
+    const int row_in_tile = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + C::kColS(t);
+    const uint32_t tO = tmem_base + lane_base + C::kColO(t);
+    const float scale_log2 = p.sm_scale * kLog2e;
+    uint32_t item_count = 0, s_count = 0, o_count = 0;
+    bool ok = true;
+    while (ok) {
+      const int slot = item_count & 1;
+      ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int item = sched_ring[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sched_empty0 + 8u * slot);
+      if (item >= sched.total_items) break;
+      ++item_count;
+      int bh, row0;
+      decode(item, bh, row0);
+      const int tile_row0 = row0 + t * kTileM;
+      const int row = tile_row0 + row_in_tile;
+      const int n_tiles = num_kv_tiles(tile_row0, S, p.causal);
+      if (n_tiles == 0) continue;
+
+      float m_used = -INFINITY;  // reference max, in raw score units
+      float l = 0.f;
+      for (int j = 0; j < n_tiles; ++j) {
+        ok = mbar_wait(bar_s_full(t), s_count & 1, abort_flag, wait_ns, kTagSFull);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        ++s_count;
+        tc_fence_after_sync();
+
+        uint32_t s0[32], s1[32], s2[32], s3[32];
+        tmem_ld_x32(tS + 0, s0);
+        tmem_ld_x32(tS + 32, s1);
+        tmem_ld_x32(tS + 64, s2);
+        tmem_ld_x32(tS + 96, s3);
+        tmem_wait_ld();
+        reg_fence_x32(s0);
+        reg_fence_x32(s1);
+        reg_fence_x32(s2);
+        reg_fence_x32(s3);
+
+        // masked tile: the one crossing the diagonal, or the ragged end of the sequence
+        const int n0 = j * kTileN;
+        const bool masked = (n0 + kTileN > S) || (p.causal && n0 + kTileN > tile_row0 + 1);
+        if (masked) {
+          int limit = S - 1 - n0;                           // last visible column of this tile
+          if (p.causal) limit = min(limit, row - n0);
+          const uint32_t ninf = 0xff800000u;
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            if (c > limit) s0[c] = ninf;
+            if (c + 32 > limit) s1[c] = ninf;
+            if (c + 64 > limit) s2[c] = ninf;
+            if (c + 96 > limit) s3[c] = ninf;
+          }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          mx0 = fmaxf(mx0, __uint_as_float(s0[c]));
+          mx1 = fmaxf(mx1, __uint_as_float(s1[c]));
+          mx2 = fmaxf(mx2, __uint_as_float(s2[c]));
+          mx3 = fmaxf(mx3, __uint_as_float(s3[c]));
+        }
+        float mb = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        if (mb == -INFINITY) mb = 0.f;  // only rows past S can get here; keep them finite
+
+        // Lazy rescale: move the reference max only when it grew by more than the threshold.
+        float alpha = 1.f;
+        bool grow = false;
+        if (j == 0) {
+          m_used = mb;
+        } else if ((mb - m_used) * scale_log2 > kRescaleThreshold) {
+          alpha = ex2((m_used - mb) * scale_log2);
+          l *= alpha;
+          m_used = mb;
+          grow = true;
+        }
+        if (__any_sync(0xffffffffu, grow)) {
+          // O_t is quiescent here: S_t(j) complete implies every earlier MMA of this tile completed.
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld_x32(tO + c0, o);
+            tmem_wait_ld();
+            reg_fence_x32(o);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+            tmem_st_x32(tO + c0, o);
+          }
+        }
+
+        const float neg_m = -m_used * scale_log2;
+        float sum0 = 0.f, sum1 = 0.f;
+        auto exp_pack_store = [&](uint32_t (&sv)[32], int chunk) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            const float e0 = ex2(fmaf(__uint_as_float(sv[c]), scale_log2, neg_m));
+            const float e1 = ex2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, neg_m));
+            sum0 += e0;
+            sum1 += e1;
+            pk[c >> 1] = pack2<kBf16>(e0, e1);
+          }
+          tmem_st_x16(tS + chunk * 16, pk);
+        };
+        exp_pack_store(s0, 0);
+        exp_pack_store(s1, 1);
+        exp_pack_store(s2, 2);
+        exp_pack_store(s3, 3);
+        l += sum0 + sum1;
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar_p_full(t));
+      }
+      if (!ok) break;
+
+      // ---- epilogue: O_t / l -> global, lse = m + log l
+      ok = mbar_wait(bar_o_full(t), o_count & 1, abort_flag, wait_ns, kTagOFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ++o_count;
+      tc_fence_after_sync();
+      const float inv_l = 1.f / l;
+      const int b = bh / p.H, h = bh - b * p.H;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_stride[0] + h * p.o_stride[1] +
+                       static_cast<int64_t>(row) * p.o_stride[2];
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t o[32];
+        tmem_ld_x32(tO + c0, o);
+        tmem_wait_ld();
+        reg_fence_x32(o);
+        if (row < S) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint4 v4;
+            v4.x = pack2<kBf16>(__uint_as_float(o[c + 0]) * inv_l, __uint_as_float(o[c + 1]) * inv_l);
+            v4.y = pack2<kBf16>(__uint_as_float(o[c + 2]) * inv_l, __uint_as_float(o[c + 3]) * inv_l);
+            v4.z = pack2<kBf16>(__uint_as_float(o[c + 4]) * inv_l, __uint_as_float(o[c + 5]) * inv_l);
+            v4.w = pack2<kBf16>(__uint_as_float(o[c + 6]) * inv_l, __uint_as_float(o[c + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c0 + c) = v4;
+          }
+        }
+      }
+      if (p.lse != nullptr && row < S)
+        p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);
+      tc_fence_before_sync();
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag != 0) {
+    // Give copies and MMAs still in flight time to land before shared memory and TMEM go away.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// [B,H,S,D] tensor, 16-bit elements, as a 4-D map (D, S, H, B) with boxes of 64 x `box_rows`.
+bool make_map(CUtensorMap* map, const void* base, const FwdParams& p, const int64_t* st, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(p.D), static_cast<cuuint64_t>(p.S),
+                              static_cast<cuuint64_t>(p.H), static_cast<cuuint64_t>(p.B)};
+  // A dimension of extent 1 may carry any stride; keep the encoder happy with a legal one.
+  auto stride_bytes = [&](int64_t s, int64_t fallback) {
+    return static_cast<cuuint64_t>((s > 0 ? s : fallback) * 2);
+  };
+  const cuuint64_t strides[3] = {stride_bytes(st[2], p.D), stride_bytes(st[1], static_cast<int64_t>(p.S) * p.D),
+                                 stride_bytes(st[0], static_cast<int64_t>(p.H) * p.S * p.D)};
+  const cuuint32_t box[4] = {64u, static_cast<cuuint32_t>(box_rows), 1u, 1u};
+  const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  const CUresult r = enc(map, p.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int D, bool kBf16>
+cudaError_t launch_one(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches) {
+  using C = Cfg<D>;
+  TmaMaps maps;
+  if (!make_map(&maps.q, p.q, p, p.q_stride, kTileM) || !make_map(&maps.k, p.k, p, p.k_stride, kTileN) ||
+      !make_map(&maps.v, p.v, p, p.v_stride, kTileN))
+    return cudaErrorInvalidValue;
+  SchedInfo sched;
+  sched.items_per_head = (p.S + kNT * kTileM - 1) / (kNT * kTileM);
+  sched.total_items = sched.items_per_head * p.B * p.H;
+  auto kern = fwd_tcgen05_kernel<D, kBf16>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  e = cudaMemsetAsync(p.tile_counter, 0, sizeof(unsigned int), stream);
+  if (e != cudaSuccess) return e;
+  const int grid = sched.total_items < sm_count ? sched.total_items : sm_count;
+  kern<<<grid, kNumThreads, C::kSmemBytes, stream>>>(maps, p, sched);
+  e = cudaGetLastError();
+  if (e == cudaSuccess) *launches += 1;
+  return e;
+}
+
+}  // namespace
+
+bool tcgen05_supports(int S, int D, float sm_scale) {
+  return (D == 64 || D == 128) && S >= 1 && sm_scale > 0.f;
+}
+
+cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches) {
+  if (p.D == 128) return p.bf16 ? launch_one<128, true>(p, sm_count, stream, launches)
+                                : launch_one<128, false>(p, sm_count, stream, launches);
+  if (p.D == 64) return p.bf16 ? launch_one<64, true>(p, sm_count, stream, launches)
+                               : launch_one<64, false>(p, sm_count, stream, launches);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace rsfa

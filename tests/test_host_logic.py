@@ -1,0 +1,105 @@
+"""Host-side logic that needs no GPU: tile table, path selection, argument errors, sharding."""
+import ctypes
+
+import pytest
+import torch
+
+import ascend_rsfa.flash_attention_forward as fa
+from ascend_rsfa import _capi, sharding
+
+lib = _capi.load()
+
+BASELINE_SHAPES = [
+    (1, 2, 128, 64), (128, 8, 2048, 128), (64, 8, 1024, 256), (16, 16, 4096, 128), (4, 32, 8192, 64),
+]
+
+
+@pytest.mark.parametrize("shape", BASELINE_SHAPES)
+@pytest.mark.parametrize("causal", [False, True])
+def test_get_tiling_covers_every_baseline_config(shape, causal):
+    bm, bn = fa.get_tiling(*shape, causal)
+    assert (bm, bn) in {(128, 128), (64, 64), (64, 32)}
+    # keyed by (S, D, causal): batch and heads do not matter (the reference raises KeyError)
+    assert fa.get_tiling(3, 5, shape[2], shape[3], causal) == (bm, bn)
+
+
+def test_get_tiling_reference_listed_shapes_do_not_raise():
+    # every tuple the reference's dict lists (flash_attention_forward.py:631-663) must resolve
+    for z, h, n, d in [(1, 1, 64, 64), (1, 1, 128, 128), (1, 2, 256, 256), (2, 2, 128, 256), (1, 2, 1024, 64),
+                       (4, 32, 64, 64), (4, 32, 128, 128), (4, 32, 256, 128), (4, 32, 512, 64),
+                       (4, 32, 1024, 64), (4, 32, 1024, 128), (4, 32, 2048, 64), (4, 32, 2048, 128),
+                       (4, 32, 4096, 64), (128, 8, 1024, 64), (128, 8, 1024, 128), (128, 8, 1024, 256),
+                       (128, 8, 2048, 128), (128, 8, 2048, 256), (128, 8, 4096, 128), (128, 8, 8192, 64)]:
+        for causal in (False, True):
+            bm, bn = fa.get_tiling(z, h, n, d, causal)
+            assert bm > 0 and bn > 0
+
+
+def test_get_tiling_rejects_impossible_shapes():
+    with pytest.raises(ValueError):
+        fa.get_tiling(1, 1, 128, 48, False)   # head dim outside {16,32,64,128,256} (:554)
+    with pytest.raises(ValueError):
+        fa.get_tiling(1, 1, 0, 64, False)
+
+
+def test_path_selection_follows_the_short_sequence_rule():
+    assert fa.select_path(128, 64, False, 0.5)[0] == _capi.RSFA_PATH_GENERIC     # N_CTX <= 128 (:564)
+    assert fa.select_path(2048, 128, True, 0.5)[0] == _capi.RSFA_PATH_TCGEN05
+    assert fa.select_path(8192, 64, False, 0.125)[0] == _capi.RSFA_PATH_TCGEN05
+    assert fa.select_path(2048, 32, False, 0.5)[0] == _capi.RSFA_PATH_GENERIC    # D = 32 not on tcgen05
+    assert fa.select_path(2048, 128, False, -0.5)[0] == _capi.RSFA_PATH_GENERIC  # non-positive scale
+    assert fa.select_path(2048, 128, False, 0.5) == (1, 128, 128)
+
+
+def test_rsfa_fwd_argument_errors_need_no_device():
+    st = (ctypes.c_int64 * 16)(*([64 * 128, 128 * 64, 64, 1] * 4))
+    ok_ptr = ctypes.c_void_p(4096)
+    f = lib.rsfa_fwd
+    bad = _capi.RSFA_ERR_INVALID_ARGUMENT
+    assert f(None, ok_ptr, ok_ptr, ok_ptr, None, 1, 1, 128, 64, st, 0, 0.5, 64, 64, 0, None) == bad
+    assert f(ok_ptr, ok_ptr, ok_ptr, ok_ptr, None, 1, 1, 128, 48, st, 0, 0.5, 64, 64, 0, None) == bad
+    assert f(ok_ptr, ok_ptr, ok_ptr, ok_ptr, None, 1, 1, 0, 64, st, 0, 0.5, 64, 64, 0, None) == bad
+    assert f(ok_ptr, ok_ptr, ok_ptr, ok_ptr, None, 1, 1, 128, 64, st, 0, 0.5, 0, 64, 0, None) == bad
+    assert f(ok_ptr, ok_ptr, ok_ptr, ok_ptr, None, 1, 1, 128, 64, st, 0, 0.5, 64, 64, 7, None) == bad
+    assert f(ctypes.c_void_p(4100), ok_ptr, ok_ptr, ok_ptr, None, 1, 1, 128, 64, st, 0, 0.5, 64, 64, 0, None) == bad
+    st_bad = (ctypes.c_int64 * 16)(*([64 * 128, 128 * 64, 60, 1] * 4))
+    assert f(ok_ptr, ok_ptr, ok_ptr, ok_ptr, None, 1, 1, 128, 64, st_bad, 0, 0.5, 64, 64, 0, None) == bad
+    assert f(ok_ptr, ok_ptr, ok_ptr, ok_ptr, None, 1, 1, 128, 64, st, 0, float("nan"), 64, 64, 0, None) == bad
+
+
+def test_attention_rejects_cpu_tensors_and_bad_shapes():
+    q = torch.zeros(1, 1, 64, 64, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        fa.attention(q, q, q, False, 0.5, 64, 64)
+    with pytest.raises(AssertionError):
+        fa.attention(torch.zeros(1, 1, 64, 48, dtype=torch.float16), q, q, False, 0.5, 64, 64)
+    with pytest.raises(TypeError):
+        fa.attention(q, q, q, causal=False, sm_scale=0.5, BM=64, BN=64)   # positional only, like Function.apply
+
+
+def test_options_round_trip():
+    fa.set_option("wait_limit_ms", 1500)
+    assert lib.rsfa_get_option(b"wait_limit_ms") == 1500
+    fa.set_option("wait_limit_ms", 2000)
+    with pytest.raises(ValueError):
+        fa.set_option("no_such_option", 1)
+    with pytest.raises(ValueError):
+        fa.set_option("force_path", 5)
+
+
+@pytest.mark.parametrize("heads,world", [(1024, 8), (512, 4), (128, 8), (2, 2), (7, 4), (3, 8)])
+def test_head_slabs_partition_exactly(heads, world):
+    slabs = [sharding.head_slab(heads, r, world) for r in range(world)]
+    assert slabs[0][0] == 0 and slabs[-1][1] == heads
+    for a, b in zip(slabs, slabs[1:]):
+        assert a[1] == b[0]
+    sizes = [hi - lo for lo, hi in slabs]
+    assert max(sizes) - min(sizes) <= 1
+
+
+def test_shard_is_a_view():
+    t = torch.arange(2 * 4 * 3 * 8, dtype=torch.float32).reshape(2, 4, 3, 8)
+    s = sharding.shard_heads(t, 1, 4)
+    assert s.shape == (1, 2, 3, 8) and s.data_ptr() == t.reshape(1, 8, 3, 8)[:, 2:].data_ptr()
+    with pytest.raises(ValueError):
+        sharding.head_slab(8, 4, 4)
