@@ -1,0 +1,219 @@
+"""Parity of the CUDA kernels with the fp32 oracle and the reference's own outputs, on a B200.
+
+Every case calls through the C ABI (ctypes -> rsfa_fwd).  Tolerance is the reference's:
+atol = rtol = 1e-2 (flash_attention_forward.py:736-738), plus a separate finiteness check
+because the reference's equal_nan=True would let NaN == NaN pass.
+"""
+import ctypes
+import math
+
+import pytest
+import torch
+
+from conftest import golden_cases, load_golden
+from oracle.attention_ref import CONFIGS, attention_fp32, error_metrics, make_inputs
+
+pytestmark = pytest.mark.gpu
+
+ATOL = RTOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def fa(cuda_device):
+    import ascend_rsfa.flash_attention_forward as mod
+
+    mod.set_option("force_path", -1)
+    yield mod
+    mod.set_option("force_path", -1)
+
+
+def check(fa, q, k, v, causal, scale, bm, bn, dev, lse=True, tol=ATOL):
+    o, M = fa.attention_with_lse(q.to(dev), k.to(dev), v.to(dev), causal, scale, bm, bn)
+    torch.cuda.synchronize()
+    fa.device_status()
+    ref, lse_ref = attention_fp32(q, k, v, causal, scale, return_lse=True)
+    m = error_metrics(o, ref, tol, tol)
+    assert m["finite"], m
+    assert m["allclose"], m
+    if lse:
+        assert torch.allclose(M.cpu(), lse_ref, atol=2e-3, rtol=2e-3)
+    return m
+
+
+@pytest.mark.parametrize("name", golden_cases())
+def test_matches_reference_outputs(fa, cuda_device, name):
+    g = load_golden(name)
+    o = fa.attention(g["q"].to(cuda_device), g["k"].to(cuda_device), g["v"].to(cuda_device),
+                     g["causal"], g["sm_scale"], g["block_m"], g["block_n"])
+    torch.cuda.synchronize()
+    m = error_metrics(o, g["o"].float(), ATOL, RTOL)
+    assert m["finite"] and m["allclose"], m
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_cfg1(fa, cuda_device, causal):
+    B, H, S, D, scale, mult = CONFIGS["cfg1"]
+    q, k, v = make_inputs(B, H, S, D, seed=42, std=mult)
+    m = check(fa, q, k, v, causal, scale, 64, 64, cuda_device)
+    assert m["max_abs"] < 4e-3
+
+
+# The reference's own test shapes (flash_attention_forward.py:671-699), N(0, 0.5), sm_scale 0.5,
+# with batch reduced where the oracle would take too long.
+REFERENCE_SHAPES = [
+    (1, 2, 1024, 64, False, 64, 32), (1, 1, 64, 64, False, 64, 16), (4, 32, 64, 64, False, 64, 32),
+    (1, 1, 128, 128, False, 16, 16), (1, 1, 128, 128, False, 64, 64), (4, 32, 128, 128, False, 32, 64),
+    (1, 2, 1024, 64, False, 128, 32), (1, 1, 64, 64, True, 64, 16), (4, 32, 64, 64, True, 64, 32),
+    (1, 1, 128, 128, True, 16, 16), (1, 1, 128, 128, True, 64, 64), (1, 2, 1024, 64, True, 64, 32),
+    (1, 1, 128, 128, True, 32, 32), (1, 2, 1024, 64, True, 128, 32), (2, 4, 2048, 128, False, 128, 128),
+    (2, 4, 4096, 64, False, 128, 128), (4, 8, 1024, 128, False, 128, 128), (4, 8, 1024, 64, False, 128, 128),
+    (2, 4, 2048, 64, True, 64, 64), (4, 8, 1024, 64, True, 64, 64), (4, 32, 512, 64, True, 64, 64),
+    (4, 32, 256, 128, True, 64, 64),
+]
+
+
+@pytest.mark.parametrize("Z,H,N,D,causal,BM,BN", REFERENCE_SHAPES)
+def test_reference_test_shapes(fa, cuda_device, Z, H, N, D, causal, BM, BN):
+    q, k, v = make_inputs(Z, H, N, D, seed=20, std=0.5)
+    m = check(fa, q, k, v, causal, 0.5, BM, BN, cuda_device)
+    assert m["max_abs"] < 4e-3  # the reference records <= 9.8e-4 on its shapes
+
+
+def test_bf16(fa, cuda_device):
+    q, k, v = make_inputs(2, 4, 1024, 64, seed=20, std=0.5, dtype=torch.bfloat16)
+    check(fa, q, k, v, False, 0.5, 128, 128, cuda_device, tol=2e-2)
+    q, k, v = make_inputs(1, 2, 512, 128, seed=21, std=0.5, dtype=torch.bfloat16)
+    check(fa, q, k, v, True, 0.5, 128, 128, cuda_device, tol=2e-2)
+    q, k, v = make_inputs(1, 2, 100, 32, seed=22, std=0.5, dtype=torch.bfloat16)
+    check(fa, q, k, v, True, 0.5, 64, 64, cuda_device, tol=2e-2)
+
+
+@pytest.mark.parametrize("D", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("causal", [False, True])
+def test_every_head_dim(fa, cuda_device, D, causal):
+    q, k, v = make_inputs(1, 3, 384, D, seed=5)
+    check(fa, q, k, v, causal, 1.0 / math.sqrt(D), 128, 128, cuda_device)
+
+
+@pytest.mark.parametrize("S", [1, 7, 63, 65, 127, 129, 255, 257, 300, 511, 640, 1000])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_ragged_sequence_lengths(fa, cuda_device, S, D, causal):
+    q, k, v = make_inputs(1, 2, S, D, seed=S)
+    check(fa, q, k, v, causal, 0.25, 128, 128, cuda_device)
+
+
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("causal", [False, True])
+def test_both_kernel_families_agree(fa, cuda_device, path, causal):
+    fa.set_option("force_path", path)
+    try:
+        for S, D in [(128, 64), (128, 128), (96, 64), (768, 128), (1536, 64)]:
+            q, k, v = make_inputs(2, 2, S, D, seed=9)
+            check(fa, q, k, v, causal, 0.3, 128, 128, cuda_device)
+    finally:
+        fa.set_option("force_path", -1)
+
+
+def test_result_does_not_depend_on_requested_tile(fa, cuda_device):
+    q, k, v = make_inputs(1, 2, 512, 64, seed=4)
+    outs = [fa.attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), True, 0.5, bm, bn)
+            for bm, bn in [(16, 16), (64, 32), (128, 64), (128, 512), (256, 256)]]
+    torch.cuda.synchronize()
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+
+
+def test_wide_logits_online_softmax_stability(fa, cuda_device):
+    # the cfg5 recipe: inputs x2 widen the logit range; also a huge-scale case that forces rescales
+    q, k, v = make_inputs(1, 2, 2048, 64, seed=8, std=2.0)
+    check(fa, q, k, v, True, 0.125, 128, 128, cuda_device)
+    check(fa, q, k, v, False, 0.125, 128, 128, cuda_device)
+    q, k, v = make_inputs(1, 1, 1024, 128, seed=8, std=1.0)
+    check(fa, q, k, v, False, 3.0, 128, 128, cuda_device)   # near one-hot rows, max keeps growing
+    # keys sorted so every tile raises the running max: exercises the in-TMEM rescale each step
+    kn = k.float().norm(dim=-1)
+    order = kn.argsort(dim=-1)
+    k2 = torch.gather(k, 2, order[..., None].expand_as(k))
+    q2 = k2.flip(2).contiguous()
+    check(fa, q2, k2, v, False, 1.0, 128, 128, cuda_device)
+
+
+def test_strided_inputs_and_views(fa, cuda_device):
+    B, H, S, D = 2, 3, 256, 64
+    big = torch.randn(B, S, 3, H, D, generator=torch.Generator().manual_seed(1)).half()
+    q, k, v = [big[:, :, i].permute(0, 2, 1, 3) for i in range(3)]   # [B,H,S,D] views, row stride 3*H*D
+    dev = cuda_device
+    bigd = big.to(dev)
+    qd, kd, vd = [bigd[:, :, i].permute(0, 2, 1, 3) for i in range(3)]
+    o = fa.attention(qd, kd, vd, True, 0.3, 128, 128)
+    torch.cuda.synchronize()
+    ref = attention_fp32(q.contiguous(), k.contiguous(), v.contiguous(), True, 0.3)
+    m = error_metrics(o, ref)
+    assert m["finite"] and m["allclose"], m
+    assert o.shape == (B, H, S, D)
+
+
+def test_requires_grad_inputs_and_no_backward(fa, cuda_device):
+    q, k, v = [t.to(cuda_device).requires_grad_() for t in make_inputs(1, 1, 256, 64, seed=2, std=0.5)]
+    o = fa.attention(q, k, v, False, 0.5, 64, 64)
+    assert o.shape == q.shape and o.dtype == q.dtype
+    with pytest.raises(NotImplementedError):
+        o.float().sum().backward()
+
+
+def test_size_independent_properties_at_full_cfg2_heads(fa, cuda_device):
+    """At BASELINE cfg2's per-head size (S=2048, D=128) on many heads: rows of P sum to one
+    (V = ones -> O = ones), causal row 0 equals v[0], and a uniform shift of the logits
+    (adding a constant vector to every key along q) leaves the output unchanged."""
+    B, H, S, D = 4, 8, 2048, 128
+    dev = cuda_device
+    g = torch.Generator(device=dev).manual_seed(0)
+    q = torch.randn(B, H, S, D, generator=g, device=dev).half()
+    k = torch.randn(B, H, S, D, generator=g, device=dev).half()
+    v = torch.randn(B, H, S, D, generator=g, device=dev).half()
+    ones = torch.ones_like(v)
+    for causal in (False, True):
+        o = fa.attention(q, k, ones, causal, 0.5, 128, 128)
+        assert torch.allclose(o.float(), torch.ones_like(o, dtype=torch.float32), atol=2e-3)
+    o = fa.attention(q, k, v, True, 0.5, 128, 128)
+    assert torch.allclose(o[:, :, 0].float(), v[:, :, 0].float(), atol=1e-3)
+    # checksum of checksums against the oracle on a sample of heads
+    sel = [(0, 0), (1, 3), (3, 7)]
+    for b, h in sel:
+        ref = attention_fp32(q[b:b + 1, h:h + 1].cpu(), k[b:b + 1, h:h + 1].cpu(), v[b:b + 1, h:h + 1].cpu(), True, 0.5)
+        m = error_metrics(o[b:b + 1, h:h + 1], ref)
+        assert m["finite"] and m["allclose"], m
+    fa.device_status()
+
+
+def test_host_buffer_entry_point(fa, cuda_device):
+    q, k, v = make_inputs(3, 5, 384, 64, seed=6)
+    fa.set_option("host_slab_heads", 4)   # 15 heads -> slabs of 4,4,4,3: exercises the double buffer
+    try:
+        o = fa.attention_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), True, 0.2, 128, 128, device=0)
+    finally:
+        fa.set_option("host_slab_heads", 0)
+    m = error_metrics(o, attention_fp32(q, k, v, True, 0.2))
+    assert m["finite"] and m["allclose"], m
+    o2 = fa.attention_host(q, k, v, False, 0.2, 128, 128, device=0)   # pageable buffers
+    m = error_metrics(o2, attention_fp32(q, k, v, False, 0.2))
+    assert m["finite"] and m["allclose"], m
+
+
+def test_device_argument_errors(fa, cuda_device):
+    q = torch.zeros(1, 1, 128, 64, dtype=torch.float16, device=cuda_device)
+    with pytest.raises(ValueError):
+        fa.attention(q, q, q, False, 0.5, 0, 64)
+    with pytest.raises(ValueError):
+        fa.attention(q, q, q.float(), False, 0.5, 64, 64)
+    assert fa.get_num_compute_cores() >= 100
+
+
+def test_launch_counter_counts_kernels(fa, cuda_device):
+    q = torch.zeros(1, 1, 256, 64, dtype=torch.float16, device=cuda_device)
+    n0 = fa.launch_count()
+    fa.attention(q, q, q, False, 0.5, 128, 128)
+    fa.attention(q, q, q, True, 0.5, 128, 128)
+    torch.cuda.synchronize()
+    assert fa.launch_count() - n0 == 2
