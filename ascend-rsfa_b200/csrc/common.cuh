@@ -23,6 +23,9 @@ struct FwdParams {
   int* status;                 // device status word, never null
   unsigned int* tile_counter;  // device work-queue counter (persistent kernel)
   unsigned long long wait_limit_ns;
+#ifdef RSFA_TRACE
+  unsigned long long* trace;  // debug builds only: per-role event log of CTA 0
+#endif
 };
 
 // Launchers implemented in the kernel translation units.  Each returns a cudaError_t

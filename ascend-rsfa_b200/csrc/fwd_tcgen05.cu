@@ -59,6 +59,26 @@ enum : int {
   kTagQEmpty = 1, kTagKvEmpty, kTagQFull, kTagKvFull, kTagPFull, kTagSFull, kTagOFull, kTagSched
 };
 
+// Debug builds (-DRSFA_TRACE) log (clock, code) pairs per role for CTA 0; the product build
+// compiles this away.
+#ifdef RSFA_TRACE
+constexpr int kTraceCap = 4096;
+#define RSFA_TRACE_DECL(role_) \
+  unsigned long long* trace_buf = (p.trace != nullptr && blockIdx.x == 0) ? p.trace + (role_) * 2 * kTraceCap : nullptr; \
+  int trace_n = 0
+#define RSFA_TRACE_EV(code_)                                         \
+  do {                                                               \
+    if (trace_buf != nullptr && trace_n < kTraceCap) {               \
+      trace_buf[2 * trace_n] = static_cast<unsigned long long>(clock64()); \
+      trace_buf[2 * trace_n + 1] = static_cast<unsigned long long>(code_); \
+      ++trace_n;                                                     \
+    }                                                                \
+  } while (0)
+#else
+#define RSFA_TRACE_DECL(role_) do {} while (0)
+#define RSFA_TRACE_EV(code_) do {} while (0)
+#endif
+
 template <int D>
 struct Cfg {
   static constexpr int kBoxes = D / 64;                       // 64-column TMA boxes per row
@@ -67,7 +87,7 @@ struct Cfg {
   static constexpr int kStages = (D == 128) ? 4 : 6;
   static constexpr int kQBoxBytes = kTileM * 128;             // 128 rows x 128 B
   static constexpr int kKvBoxBytes = kTileN * 128;
-  static constexpr int kNumBarriers = 2 * kNT + 2 * kStages + 3 * kNT + 4;
+  static constexpr int kNumBarriers = 2 * kNT + 2 * kStages + 4 * kNT + 4;
   static constexpr int kSmemBytes = kNT * kQTileBytes + kStages * kKvTileBytes + 1024 /*align*/ +
                                     kNumBarriers * 8 + 64;
   __host__ __device__ static constexpr int kColS(int t) { return t * kTileN; }
@@ -100,6 +120,32 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// Two fp32 lanes in one 64-bit register: Blackwell's packed FFMA2 / FADD2 halve the issue slots
+// of the scale-and-subtract and of the row sum.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 // Number of key tiles Q tile (row0 .. row0+127) has to visit.
 __device__ __forceinline__ int num_kv_tiles(int row0, int S, int causal) {
   if (row0 >= S) return 0;
@@ -123,9 +169,10 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   auto bar_kv_full = [&](int s) { return sBar + 8u * (2 * kNT + s); };
   auto bar_kv_empty = [&](int s) { return sBar + 8u * (2 * kNT + C::kStages + s); };
   auto bar_s_full = [&](int t) { return sBar + 8u * (2 * kNT + 2 * C::kStages + t); };
-  auto bar_p_full = [&](int t) { return sBar + 8u * (3 * kNT + 2 * C::kStages + t); };
-  auto bar_o_full = [&](int t) { return sBar + 8u * (4 * kNT + 2 * C::kStages + t); };
-  const uint32_t bar_sched_full0 = sBar + 8u * (5 * kNT + 2 * C::kStages);  // 2 slots
+  // P_t is handed to the MMA warp in two halves of 64 keys so the first PV MMAs start early.
+  auto bar_p_full = [&](int t, int half) { return sBar + 8u * (3 * kNT + 2 * C::kStages + 2 * t + half); };
+  auto bar_o_full = [&](int t) { return sBar + 8u * (5 * kNT + 2 * C::kStages + t); };
+  const uint32_t bar_sched_full0 = sBar + 8u * (6 * kNT + 2 * C::kStages);  // 2 slots
   const uint32_t bar_sched_empty0 = bar_sched_full0 + 16u;                   // 2 slots
   const uint32_t misc = sBar + 8u * C::kNumBarriers;
   // misc words: [0] TMEM base, [1] abort flag, [2..3] scheduler ring
@@ -144,7 +191,8 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       mbar_init(bar_q_full(t), 1);
       mbar_init(bar_q_empty(t), 1);
       mbar_init(bar_s_full(t), 1);
-      mbar_init(bar_p_full(t), kTileM);
+      mbar_init(bar_p_full(t, 0), kTileM);
+      mbar_init(bar_p_full(t, 1), kTileM);
       mbar_init(bar_o_full(t), 1);
     }
     for (int s = 0; s < C::kStages; ++s) {
@@ -185,6 +233,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   if (warp == kTmaWarp) {
     // ================================================================ producer
     if (lane == 0) {
+      RSFA_TRACE_DECL(3);
       uint32_t kv_count = 0;   // K/V tiles loaded so far (ring position)
       uint32_t item_count = 0; // work items started so far
       bool ok = true;
@@ -207,6 +256,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
 
         auto load_q = [&](int t) -> bool {
           if (!mbar_wait(bar_q_empty(t), (item_count & 1) ^ 1, abort_flag, wait_ns, kTagQEmpty)) return false;
+          RSFA_TRACE_EV(0x100 + t);
           mbar_arrive_expect_tx(bar_q_full(t), C::kQTileBytes);
           for (int bx = 0; bx < C::kBoxes; ++bx)
             tma_load_4d(sQ + t * C::kQTileBytes + bx * C::kQBoxBytes, &maps.q, bar_q_full(t), bx * 64,
@@ -217,6 +267,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           const uint32_t s = kv_count % C::kStages;
           const uint32_t ph = (kv_count / C::kStages) & 1;
           if (!mbar_wait(bar_kv_empty(s), ph ^ 1, abort_flag, wait_ns, kTagKvEmpty)) return false;
+          RSFA_TRACE_EV(0x200 + j);
           mbar_arrive_expect_tx(bar_kv_full(s), C::kKvTileBytes);
           for (int bx = 0; bx < C::kBoxes; ++bx)
             tma_load_4d(sKV + s * C::kKvTileBytes + bx * C::kKvBoxBytes, map, bar_kv_full(s), bx * 64,
@@ -224,10 +275,12 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           ++kv_count;
           return true;
         };
-        ok = load_q(0);
-        if (ok && nmax > 0) ok = load_kv(&maps.k, 0);
-        if (ok) ok = load_q(1);
+        // K_0 / V_0 first: their ring slots free up while the previous item drains, whereas the
+        // Q buffers are released only once that item's last QK^T MMA has finished.
+        if (nmax > 0) ok = load_kv(&maps.k, 0);
         if (ok && nmax > 0) ok = load_kv(&maps.v, 0);
+        if (ok) ok = load_q(0);
+        if (ok) ok = load_q(1);
         for (int j = 1; ok && j < nmax; ++j) {
           ok = load_kv(&maps.k, j);
           if (ok) ok = load_kv(&maps.v, j);
@@ -240,6 +293,10 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_f16(kTileM, kTileN, kBf16, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(kTileM, D, kBf16, false, true);
+      RSFA_TRACE_DECL(2);
+      const uint64_t desc_q0 = make_smem_desc_sw128(sQ, 16, 1024);
+      const uint64_t desc_k0 = make_smem_desc_sw128(sKV, 16, 1024);
+      const uint64_t desc_v0 = make_smem_desc_sw128(sKV, C::kKvBoxBytes, 1024);
       uint32_t kv_count = 0, item_count = 0;
       uint32_t p_count[kNT] = {0, 0};
       bool ok = true;
@@ -258,27 +315,26 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           n[t] = num_kv_tiles(row0 + t * kTileM, S, p.causal);
           nmax = max(nmax, n[t]);
         }
-        // S_t = Q_t K^T : both operands K-major, 64-column boxes, 8-row atoms of 1024 B
+        // S_t = Q_t K^T : both operands K-major, 64-column boxes, 8-row atoms of 1024 B.  A step
+        // of 16 along D moves the start address by 32 B inside the 128-byte swizzle row.
         auto issue_qk = [&](int t, uint32_t kslot) {
-          const uint32_t qa = sQ + t * C::kQTileBytes;
-          const uint32_t ka = sKV + kslot * C::kKvTileBytes;
+          const uint64_t qd = desc_q0 + static_cast<uint64_t>((t * C::kQTileBytes) >> 4);
+          const uint64_t kd = desc_k0 + static_cast<uint64_t>((kslot * C::kKvTileBytes) >> 4);
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off_q = (ks >> 2) * C::kQBoxBytes + (ks & 3) * 32;
-            const uint32_t off_k = (ks >> 2) * C::kKvBoxBytes + (ks & 3) * 32;
-            umma_ss(tmem_base + C::kColS(t), make_smem_desc_sw128(qa + off_q, 16, 1024),
-                    make_smem_desc_sw128(ka + off_k, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+            const uint32_t off_q = ((ks >> 2) * C::kQBoxBytes + (ks & 3) * 32) >> 4;
+            const uint32_t off_k = ((ks >> 2) * C::kKvBoxBytes + (ks & 3) * 32) >> 4;
+            umma_ss(tmem_base + C::kColS(t), qd + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
           }
         };
         // O_t (+)= P_t V : A = P_t in TMEM (16 keys = 8 columns per step), B = V MN-major:
         // 16 keys per step = two 8-row atoms (stride 1024 B), 64-column boxes kKvBoxBytes apart.
-        auto issue_pv = [&](int t, uint32_t vslot, bool accumulate) {
-          const uint32_t va = sKV + vslot * C::kKvTileBytes;
+        auto issue_pv = [&](int t, uint32_t vslot, bool accumulate, int ks_begin, int ks_end) {
+          const uint64_t vd = desc_v0 + static_cast<uint64_t>((vslot * C::kKvTileBytes) >> 4);
 #pragma unroll
-          for (int ks = 0; ks < kTileN / 16; ++ks) {
-            umma_ts(tmem_base + C::kColO(t), tmem_base + C::kColS(t) + ks * 8,
-                    make_smem_desc_sw128(va + ks * 2048, C::kKvBoxBytes, 1024), idesc_pv,
-                    (accumulate || ks > 0) ? 1u : 0u);
+          for (int ks = ks_begin; ks < ks_end; ++ks) {
+            umma_ts(tmem_base + C::kColO(t), tmem_base + C::kColS(t) + ks * 8, vd + ((ks * 2048) >> 4),
+                    idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
           }
         };
         auto wait_kv = [&](uint32_t idx) -> bool {
@@ -299,6 +355,9 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
               issue_qk(t, base % C::kStages);
               umma_commit(bar_s_full(t));
             }
+            // Q_t is dead once its last QK^T MMA has run: release it so the next item's Q load
+            // overlaps the rest of this item.
+            if (n[t] <= 1) umma_commit(bar_q_empty(t));
           }
           umma_commit(bar_kv_empty(base % C::kStages));
         }
@@ -307,14 +366,23 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           const uint32_t kidx = base + 2 * j + 2;
           ok = wait_kv(vidx);
           if (!ok) break;
+          RSFA_TRACE_EV(0x6000 + j);                  // V_j present
           bool k_ready = false;
           for (int t = 0; ok && t < kNT; ++t) {
             if (j < n[t]) {
-              ok = mbar_wait(bar_p_full(t), p_count[t] & 1, abort_flag, wait_ns, kTagPFull);
+              ok = mbar_wait(bar_p_full(t, 0), p_count[t] & 1, abort_flag, wait_ns, kTagPFull);
+              if (!ok) break;
+              tc_fence_after_sync();
+              RSFA_TRACE_EV(0x1000 + (t << 8) + j);   // P half 0 seen
+              issue_pv(t, vidx % C::kStages, j > 0, 0, kTileN / 32);
+              RSFA_TRACE_EV(0x2000 + (t << 8) + j);   // PV half 0 issued
+              ok = mbar_wait(bar_p_full(t, 1), p_count[t] & 1, abort_flag, wait_ns, kTagPFull);
               if (!ok) break;
               ++p_count[t];
               tc_fence_after_sync();
-              issue_pv(t, vidx % C::kStages, j > 0);
+              RSFA_TRACE_EV(0x3000 + (t << 8) + j);   // P half 1 seen
+              issue_pv(t, vidx % C::kStages, true, kTileN / 32, kTileN / 16);
+              RSFA_TRACE_EV(0x4000 + (t << 8) + j);   // PV half 1 issued
               if (j == n[t] - 1) umma_commit(bar_o_full(t));
             }
             if (j + 1 < n[t]) {
@@ -326,6 +394,8 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
               }
               issue_qk(t, kidx % C::kStages);
               umma_commit(bar_s_full(t));
+              RSFA_TRACE_EV(0x5000 + (t << 8) + j);   // QK(j+1) issued
+              if (j + 2 == n[t]) umma_commit(bar_q_empty(t));
             }
           }
           if (!ok) break;
@@ -339,7 +409,6 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           }
         }
         if (!ok) break;
-        for (int t = 0; t < kNT; ++t) umma_commit(bar_q_empty(t));
         kv_count += 2 * nmax;
         ++item_count;
       }
@@ -354,6 +423,11 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
     const float scale_log2 = p.sm_scale * kLog2e;
     uint32_t item_count = 0, s_count = 0, o_count = 0;
     bool ok = true;
+#ifdef RSFA_TRACE
+    unsigned long long* trace_buf = (p.trace != nullptr && blockIdx.x == 0 && (warp & 3) == 0 && lane == 0)
+                                        ? p.trace + t * 2 * kTraceCap : nullptr;
+    int trace_n = 0;
+#endif
     while (ok) {
       const int slot = item_count & 1;
       ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
@@ -379,6 +453,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         if (!ok) break;
         ++s_count;
         tc_fence_after_sync();
+        RSFA_TRACE_EV(0x1000 + j);   // S seen
 
         uint32_t s0[32], s1[32], s2[32], s3[32];
         tmem_ld_x32(tS + 0, s0);
@@ -390,6 +465,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         reg_fence_x32(s1);
         reg_fence_x32(s2);
         reg_fence_x32(s3);
+        RSFA_TRACE_EV(0x2000 + j);   // S in registers
 
         // masked tile: the one crossing the diagonal, or the ragged end of the sequence
         const int n0 = j * kTileN;
@@ -408,13 +484,13 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         }
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          mx0 = fmaxf(mx0, __uint_as_float(s0[c]));
-          mx1 = fmaxf(mx1, __uint_as_float(s1[c]));
-          mx2 = fmaxf(mx2, __uint_as_float(s2[c]));
-          mx3 = fmaxf(mx3, __uint_as_float(s3[c]));
+        for (int c = 0; c < 32; c += 2) {
+          mx0 = max3(mx0, __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
+          mx1 = max3(mx1, __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
+          mx2 = max3(mx2, __uint_as_float(s2[c]), __uint_as_float(s2[c + 1]));
+          mx3 = max3(mx3, __uint_as_float(s3[c]), __uint_as_float(s3[c + 1]));
         }
-        float mb = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        float mb = fmaxf(max3(mx0, mx1, mx2), mx3);
         if (mb == -INFINITY) mb = 0.f;  // only rows past S can get here; keep them finite
 
         // Lazy rescale: move the reference max only when it grew by more than the threshold.
@@ -442,28 +518,43 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           }
         }
 
+        RSFA_TRACE_EV(0x3000 + j);   // max done
+        const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
         const float neg_m = -m_used * scale_log2;
-        float sum0 = 0.f, sum1 = 0.f;
+        const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
+        uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
         auto exp_pack_store = [&](uint32_t (&sv)[32], int chunk) {
           uint32_t pk[16];
 #pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            const float e0 = ex2(fmaf(__uint_as_float(sv[c]), scale_log2, neg_m));
-            const float e1 = ex2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, neg_m));
-            sum0 += e0;
-            sum1 += e1;
+          for (int c = 0; c < 32; c += 4) {
+            float x0, x1, x2, x3;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3])), scale2, neg_m2), x2, x3);
+            const float e0 = ex2(x0), e1 = ex2(x1), e2 = ex2(x2), e3 = ex2(x3);
+            sum_a = add_f32x2(sum_a, pack_f32x2(e0, e1));
+            sum_b = add_f32x2(sum_b, pack_f32x2(e2, e3));
             pk[c >> 1] = pack2<kBf16>(e0, e1);
+            pk[(c >> 1) + 1] = pack2<kBf16>(e2, e3);
           }
           tmem_st_x16(tS + chunk * 16, pk);
         };
         exp_pack_store(s0, 0);
         exp_pack_store(s1, 1);
-        exp_pack_store(s2, 2);
-        exp_pack_store(s3, 3);
-        l += sum0 + sum1;
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(bar_p_full(t));
+        mbar_arrive(bar_p_full(t, 0));
+        RSFA_TRACE_EV(0x4000 + j);   // half 0 handed over
+        exp_pack_store(s2, 2);
+        exp_pack_store(s3, 3);
+        {
+          float a0, a1;
+          unpack_f32x2(add_f32x2(sum_a, sum_b), a0, a1);
+          l += a0 + a1;
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar_p_full(t, 1));
+        RSFA_TRACE_EV(0x5000 + j);   // half 1 handed over
       }
       if (!ok) break;
 
@@ -473,6 +564,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       if (!ok) break;
       ++o_count;
       tc_fence_after_sync();
+      RSFA_TRACE_EV(0x6000);         // O complete seen
       const float inv_l = 1.f / l;
       const int b = bh / p.H, h = bh - b * p.H;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_stride[0] + h * p.o_stride[1] +
@@ -498,6 +590,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       if (p.lse != nullptr && row < S)
         p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);
       tc_fence_before_sync();
+      RSFA_TRACE_EV(0x7000);         // epilogue done
     }
   }
 

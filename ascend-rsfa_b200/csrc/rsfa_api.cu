@@ -38,6 +38,9 @@ std::atomic<long long> g_launches{0};
 std::atomic<long long> g_force_path{-1};
 std::atomic<long long> g_wait_limit_ms{2000};
 std::atomic<long long> g_host_slab_heads{0};
+#ifdef RSFA_TRACE
+std::atomic<long long> g_trace_ptr{0};
+#endif
 
 int ensure_device(int device, DeviceState** out) {
   if (device < 0 || device >= kMaxDevices) return RSFA_ERR_INVALID_ARGUMENT;
@@ -125,6 +128,12 @@ int rsfa_set_option(const char* name, long long value) {
     g_wait_limit_ms.store(value);
     return RSFA_OK;
   }
+#ifdef RSFA_TRACE
+  if (std::strcmp(name, "trace_ptr") == 0) {
+    g_trace_ptr.store(value);
+    return RSFA_OK;
+  }
+#endif
   if (std::strcmp(name, "host_slab_heads") == 0) {
     if (value < 0) return RSFA_ERR_INVALID_ARGUMENT;
     g_host_slab_heads.store(value);
@@ -245,6 +254,9 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
     p.tile_counter = d->counters + (d->next_slot++ % kCounterSlots);
   }
   p.wait_limit_ns = static_cast<unsigned long long>(g_wait_limit_ms.load()) * 1000000ull;
+#ifdef RSFA_TRACE
+  p.trace = reinterpret_cast<unsigned long long*>(g_trace_ptr.load());
+#endif
 
   long long launches = 0;
   cudaError_t e;
