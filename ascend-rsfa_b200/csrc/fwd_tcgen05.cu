@@ -18,6 +18,8 @@
 //   warp  8      TMA producer (one lane): Q tiles once per work item, K/V tiles
 //                through a ring of kStages shared-memory slots
 //   warp  9      MMA issuer (one lane) and owner of the TMEM allocation
+//   warps 10,11  idle; they complete the third warpgroup so that register budgets can be moved
+//                between warpgroups with setmaxnreg (softmax threads keep a whole row in registers)
 // Per key tile j and Q tile t:
 //   S_t = Q_t K_j^T          tcgen05.mma, both operands from shared memory
 //   softmax group t          tcgen05.ld S_t -> running max, exp2, row sum -> P_t
@@ -47,7 +49,7 @@ namespace {
 constexpr int kTileM = 128;   // rows per Q tile (= TMEM lanes)
 constexpr int kTileN = 128;   // keys per K/V tile
 constexpr int kNT = 2;        // Q tiles per CTA
-constexpr int kNumThreads = 320;
+constexpr int kNumThreads = 384;  // 3 warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
 constexpr int kTmaWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kTmemCols = 512;
@@ -146,6 +148,19 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   return r;
 }
 
+// Register budgets per warpgroup after the common set-up (launch allocates 168 each):
+// 2 x 128 x 208 + 128 x 80 = 63488 of 65536, so the increase never waits on an exact fit.
+constexpr int kRegsSoftmax = 208;
+constexpr int kRegsOther = 80;
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
 // Number of key tiles Q tile (row0 .. row0+127) has to visit.
 __device__ __forceinline__ int num_kv_tiles(int row0, int S, int causal) {
   if (row0 >= S) return 0;
@@ -230,7 +245,13 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
     row0 = blk * (kNT * kTileM);
   };
 
-  if (warp == kTmaWarp) {
+  // setmaxnreg is warpgroup-aligned: every warp of a warpgroup must execute the SAME instruction,
+  // so the third warpgroup lowers its budget before it splits into roles.
+  if (warp >= kTmaWarp) {
+    setmaxnreg_dec<kRegsOther>();
+  if (warp > kMmaWarp) {
+    // idle warps of the third warpgroup
+  } else if (warp == kTmaWarp) {
     // ================================================================ producer
     if (lane == 0) {
       RSFA_TRACE_DECL(3);
@@ -413,8 +434,10 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         ++item_count;
       }
     }
+  }
   } else {
     // ========================================================== softmax groups
+    setmaxnreg_inc<kRegsSoftmax>();
     const int t = warp >> 2;                   // Q tile of this group
     const int row_in_tile = (warp & 3) * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -466,6 +489,10 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         reg_fence_x32(s2);
         reg_fence_x32(s3);
         RSFA_TRACE_EV(0x2000 + j);   // S in registers
+#ifdef RSFA_TRACE
+        { uint32_t tmp; asm volatile("mov.b32 %0, %1;" : "=r"(tmp) : "r"(s0[0])); RSFA_TRACE_EV(0x8000 + j);
+          asm volatile("mov.b32 %0, %1;" : "=r"(tmp) : "r"(s3[31])); RSFA_TRACE_EV(0x9000 + j); }
+#endif
 
         // masked tile: the one crossing the diagonal, or the ragged end of the sequence
         const int n0 = j * kTileN;
@@ -482,16 +509,28 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
             if (c + 96 > limit) s3[c] = ninf;
           }
         }
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+        float mb;
+        {
+          float mx[8];
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          mx0 = max3(mx0, __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
-          mx1 = max3(mx1, __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
-          mx2 = max3(mx2, __uint_as_float(s2[c]), __uint_as_float(s2[c + 1]));
-          mx3 = max3(mx3, __uint_as_float(s3[c]), __uint_as_float(s3[c + 1]));
+          for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            mx[0] = max3(mx[0], __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
+            mx[1] = max3(mx[1], __uint_as_float(s0[c + 2]), __uint_as_float(s0[c + 3]));
+            mx[2] = max3(mx[2], __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
+            mx[3] = max3(mx[3], __uint_as_float(s1[c + 2]), __uint_as_float(s1[c + 3]));
+            mx[4] = max3(mx[4], __uint_as_float(s2[c]), __uint_as_float(s2[c + 1]));
+            mx[5] = max3(mx[5], __uint_as_float(s2[c + 2]), __uint_as_float(s2[c + 3]));
+            mx[6] = max3(mx[6], __uint_as_float(s3[c]), __uint_as_float(s3[c + 1]));
+            mx[7] = max3(mx[7], __uint_as_float(s3[c + 2]), __uint_as_float(s3[c + 3]));
+          }
+          mb = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
         }
-        float mb = fmaxf(max3(mx0, mx1, mx2), mx3);
         if (mb == -INFINITY) mb = 0.f;  // only rows past S can get here; keep them finite
+#ifdef RSFA_TRACE
+        { uint32_t tmp; asm volatile("mov.b32 %0, %1;" : "=r"(tmp) : "r"(__float_as_uint(mb))); RSFA_TRACE_EV(0xa000 + j); }
+#endif
 
         // Lazy rescale: move the reference max only when it grew by more than the threshold.
         float alpha = 1.f;

@@ -62,7 +62,7 @@ enum : int {
 // of the CTA: the first role whose wait runs out sets it, every other role sees
 // it at its next poll and leaves as well.  Returns false when the caller must
 // stop.  `tag` identifies the waiting site in the status word.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                             uint64_t limit_ns, int tag) {
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
