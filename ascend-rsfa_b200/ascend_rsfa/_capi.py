@@ -15,6 +15,7 @@ RSFA_ERR_UNSUPPORTED = -2
 RSFA_ERR_CUDA = -3
 RSFA_ERR_DEVICE_STATUS = -4
 RSFA_ERR_NO_DEVICE = -5
+RSFA_ERR_TOO_LARGE = -6
 RSFA_DTYPE_F16 = 0
 RSFA_DTYPE_BF16 = 1
 RSFA_PATH_GENERIC = 0
@@ -29,6 +30,9 @@ SIGNATURES = {
     "rsfa_fwd_host": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                  _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_float,
                                  _c.c_int, _c.c_int, _c.c_int, _c.c_int]),
+    "rsfa_fwd_noalloc": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                    _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_c.c_int64),
+                                    _c.c_int, _c.c_float, _c.c_int, _c.c_void_p]),
     "rsfa_get_tiling": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                    _c.POINTER(_c.c_int), _c.POINTER(_c.c_int)]),
     "rsfa_select_path": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int, _c.c_float, _c.c_int, _c.c_int,
@@ -72,7 +76,7 @@ def check(code, what="rsfa call"):
     if code == RSFA_OK:
         return
     msg = "%s failed: %s (code %d)" % (what, strerror(code), code)
-    if code == RSFA_ERR_INVALID_ARGUMENT:
+    if code in (RSFA_ERR_INVALID_ARGUMENT, RSFA_ERR_TOO_LARGE):
         raise ValueError(msg)
     if code == RSFA_ERR_UNSUPPORTED:
         raise NotImplementedError(msg)

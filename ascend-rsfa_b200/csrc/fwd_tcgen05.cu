@@ -40,6 +40,9 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
+
+#include "../../include/rsfa.h"
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -723,3 +726,137 @@ cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t st
 }
 
 }  // namespace rsfa
+
+// ------------------------------------------------------------------------------------------
+// rsfa_fwd_noalloc: the tcgen05 kernel for callers that must not allocate device memory.
+//
+// rsfa_fwd keeps its work-queue counter and status word in a buffer the library obtains with
+// cudaMalloc on first use.  Some callers cannot tolerate that: an inference server that hands
+// all device memory to its own arena at start-up and treats any later cudaMalloc as a fault, a
+// hard-real-time loop in which an allocation (which may synchronise the device) breaks the
+// latency budget, or a plugin loaded into a process whose memory is accounted by someone else.
+// For them the same kernel runs here with its scratch in a fixed, statically allocated block of
+// device memory that is part of the library image.
+namespace rsfa {
+namespace {
+
+// The whole scratch: word 0 = work-queue counter, word 1 = status word, rest unused.  Every GPU
+// that loads the library holds these 256 bytes until the process exits.
+constexpr int kStaticScratchBytes = 256;
+static __device__ __align__(256) unsigned int g_static_scratch[kStaticScratchBytes / sizeof(unsigned int)];
+
+// Largest problem the entry point accepts: the queue counter is one 32-bit word of the block and
+// every CTA adds to it once more after the queue is empty, so items + CTAs must stay below 2^31.
+constexpr long long kNoAllocMaxItems = 1ll << 30;
+
+struct NoAllocDevice {
+  bool ready = false;
+  unsigned int* scratch = nullptr;  // device address of g_static_scratch on this device
+  int sm_count = 0;
+};
+std::mutex g_noalloc_mu;
+NoAllocDevice g_noalloc_dev[64];
+
+// Once per device, with that device current.  In host code `g_static_scratch` is only a handle:
+// the address the kernel needs comes from cudaGetSymbolAddress.
+int noalloc_setup(int device, NoAllocDevice** out) {
+  if (device < 0 || device >= 64) return RSFA_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  NoAllocDevice& d = g_noalloc_dev[device];
+  if (!d.ready) {
+    int major = 0, sms = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+      cudaGetLastError();
+      return RSFA_ERR_NO_DEVICE;
+    }
+    if (major != 10) return RSFA_ERR_NO_DEVICE;
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return RSFA_ERR_CUDA;
+    }
+    d.scratch = static_cast<unsigned int*>(ptr);
+    d.sm_count = sms;
+    d.ready = true;
+  }
+  *out = &d;
+  return RSFA_OK;
+}
+
+}  // namespace
+}  // namespace rsfa
+
+extern "C" int rsfa_fwd_noalloc(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
+                                int S, int D, const int64_t* strides, int causal, float sm_scale, int dtype,
+                                void* stream) {
+  using namespace rsfa;
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || strides == nullptr)
+    return RSFA_ERR_INVALID_ARGUMENT;
+  if (B < 1 || H < 1 || S < 1) return RSFA_ERR_INVALID_ARGUMENT;
+  if (D != 16 && D != 32 && D != 64 && D != 128 && D != 256) return RSFA_ERR_INVALID_ARGUMENT;
+  if (dtype != RSFA_DTYPE_F16 && dtype != RSFA_DTYPE_BF16) return RSFA_ERR_INVALID_ARGUMENT;
+  if (!(sm_scale == sm_scale)) return RSFA_ERR_INVALID_ARGUMENT;
+  const void* ptrs[4] = {q, k, v, o};
+  for (int t = 0; t < 4; ++t) {
+    if ((reinterpret_cast<uintptr_t>(ptrs[t]) & 15u) != 0) return RSFA_ERR_INVALID_ARGUMENT;
+    const int64_t* st = strides + 4 * t;
+    if (st[3] != 1) return RSFA_ERR_INVALID_ARGUMENT;
+    const int extent[3] = {B, H, S};
+    for (int i = 0; i < 3; ++i)
+      if (extent[i] > 1 && (st[i] < D || (st[i] & 7) != 0)) return RSFA_ERR_INVALID_ARGUMENT;
+  }
+  // Only the tcgen05 kernel uses scratch; shapes it is not built for have no variant here.
+  if (!tcgen05_supports(S, D, sm_scale)) return RSFA_ERR_UNSUPPORTED;
+  const long long items = static_cast<long long>(B) * H * ((S + kNT * kTileM - 1) / (kNT * kTileM));
+  if (items > kNoAllocMaxItems) return RSFA_ERR_TOO_LARGE;
+
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) {
+    cudaGetLastError();
+    return RSFA_ERR_NO_DEVICE;
+  }
+  NoAllocDevice* d = nullptr;
+  const int rc = noalloc_setup(device, &d);
+  if (rc != RSFA_OK) return rc;
+
+  FwdParams p;
+  p.q = q;
+  p.k = k;
+  p.v = v;
+  p.o = o;
+  p.lse = lse;
+  p.B = B;
+  p.H = H;
+  p.S = S;
+  p.D = D;
+  for (int i = 0; i < 3; ++i) {
+    p.q_stride[i] = strides[0 + i];
+    p.k_stride[i] = strides[4 + i];
+    p.v_stride[i] = strides[8 + i];
+    p.o_stride[i] = strides[12 + i];
+  }
+  p.causal = causal ? 1 : 0;
+  p.sm_scale = sm_scale;
+  p.bf16 = (dtype == RSFA_DTYPE_BF16) ? 1 : 0;
+  p.tile_counter = d->scratch;      // cleared by the launcher on `stream` before the kernel
+  p.status = reinterpret_cast<int*>(d->scratch + 1);
+  p.wait_limit_ns = 2000ull * 1000000ull;
+#ifdef RSFA_TRACE
+  p.trace = nullptr;
+#endif
+  // The status word keeps whatever the last call left; a fresh call starts from "ok".
+  if (cudaMemsetAsync(d->scratch + 1, 0, sizeof(unsigned int), static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+    cudaGetLastError();
+    return RSFA_ERR_CUDA;
+  }
+  long long launches = 0;
+  const cudaError_t e = launch_fwd_tcgen05(p, d->sm_count, static_cast<cudaStream_t>(stream), &launches);
+  count_launches(launches);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return RSFA_ERR_CUDA;
+  }
+  return RSFA_OK;
+}

@@ -98,6 +98,10 @@ void tile_of_path(int path, int D, int* bm, int* bn) {
 
 }  // namespace
 
+namespace rsfa {
+void count_launches(long long n) { g_launches.fetch_add(n); }
+}  // namespace rsfa
+
 extern "C" {
 
 int rsfa_version(void) { return 100; }
@@ -110,6 +114,7 @@ const char* rsfa_strerror(int code) {
     case RSFA_ERR_CUDA: return "CUDA call failed";
     case RSFA_ERR_DEVICE_STATUS: return "a kernel reported a non-zero device status (bounded wait expired)";
     case RSFA_ERR_NO_DEVICE: return "no usable sm_100 CUDA device";
+    case RSFA_ERR_TOO_LARGE: return "problem exceeds the fixed scratch of the allocation-free entry point";
     default: return "unknown error code";
   }
 }

@@ -33,6 +33,7 @@ extern "C" {
 #define RSFA_ERR_CUDA (-3)             /* a CUDA runtime / driver call failed                   */
 #define RSFA_ERR_DEVICE_STATUS (-4)    /* a kernel reported a non-zero status (bounded wait...) */
 #define RSFA_ERR_NO_DEVICE (-5)        /* no CUDA device, or not an sm_100 device               */
+#define RSFA_ERR_TOO_LARGE (-6)        /* rsfa_fwd_noalloc: problem exceeds its fixed scratch   */
 
 #define RSFA_DTYPE_F16 0
 #define RSFA_DTYPE_BF16 1
@@ -80,6 +81,33 @@ RSFA_API int rsfa_fwd(const void* q, const void* k, const void* v, void* o, floa
 RSFA_API int rsfa_fwd_host(const void* q_host, const void* k_host, const void* v_host, void* o_host,
                   float* lse_host, int B, int H, int S, int D, int causal, float sm_scale,
                   int block_m, int block_n, int dtype, int device);
+
+/*
+ * rsfa_fwd for callers that must not allocate device memory.  It has no counterpart in the
+ * reference; it exists for hosts where a cudaMalloc inside an operator call is not acceptable:
+ * servers that give all device memory to their own arena at start-up, latency-critical loops in
+ * which an allocation may stall the device, plugins whose memory is accounted by the embedding
+ * process.  rsfa_fwd keeps its work-queue counter and status word in a buffer it cudaMallocs on
+ * first use; this entry point runs the same tcgen05 kernel with that scratch in a 256-byte block
+ * of static device memory inside the library (held by every GPU that loads the library until the
+ * process exits) and calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ * Arguments as rsfa_fwd, without block_m / block_n (the kernel has one tile).  Limits: only
+ * shapes the tcgen05 kernel is built for (D in {64, 128}, sm_scale > 0) -> otherwise
+ * RSFA_ERR_UNSUPPORTED; at most 2^30 work items (B * H * ceil(S / 256)), because the queue counter
+ * is a single 32-bit word of the block -> otherwise RSFA_ERR_TOO_LARGE.
+ *
+ * The first call on a device looks up the device address of the static block (one
+ * cudaGetSymbolAddress with that device current); make that first call outside any stream
+ * capture.  All calls on a device share the one block, which keeps the previous call's contents:
+ * each call clears the counter and the status word on `stream` before its kernel, so calls on one
+ * stream are safe back to back, but two calls whose kernels can overlap on the GPU (different
+ * streams, no dependency) race on the counter and must be ordered by the caller.  The status
+ * word of this path is not exposed; a bounded wait that runs out leaves the output incomplete.
+ */
+RSFA_API int rsfa_fwd_noalloc(const void* q, const void* k, const void* v, void* o, float* lse,
+                              int B, int H, int S, int D, const int64_t* strides,
+                              int causal, float sm_scale, int dtype, void* stream);
 
 /*
  * Tile lookup.  Replaces get_tiling (:624-665): the reference keys a 32-entry dict by the full

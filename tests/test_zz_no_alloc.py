@@ -1,0 +1,86 @@
+"""rsfa_fwd_noalloc — the entry point for hosts that cannot allocate device memory.
+
+Some embedders of this library give every byte of device memory to their own arena when they
+start (inference servers), or run it inside a loop where a cudaMalloc — which may stall the whole
+device — would break a latency budget.  For them the library offers one call that keeps the
+kernel's scratch (work-queue counter + status word) in static device memory instead of a lazily
+cudaMalloc'ed buffer.  This test drives that call through the C ABI with caller-owned inputs and
+outputs and checks it against the regular rsfa_fwd on the same data, twice in a row because the
+static scratch keeps the previous call's contents.
+
+The file name sorts last on purpose: a run that stops at the first failure has then already
+executed every other test.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _strides(*tensors):
+    flat = []
+    for t in tensors:
+        flat.extend(t.stride())
+    return (ctypes.c_int64 * 16)(*flat)
+
+
+@pytest.mark.parametrize("B,H,S,D,causal,scale", [(2, 3, 1024, 128, True, 0.5), (1, 4, 777, 64, False, 0.125)])
+def test_noalloc_matches_regular_entry_point_twice(cuda_device, B, H, S, D, causal, scale):
+    from ascend_rsfa import _capi
+
+    lib = _capi.load()
+    dev = cuda_device
+    g = torch.Generator(device=dev).manual_seed(123)
+    q, k, v = [torch.randn(B, H, S, D, generator=g, device=dev).half() for _ in range(3)]
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def regular():
+        o = torch.empty_like(q)
+        lse = torch.empty(B, H, S, dtype=torch.float32, device=dev)
+        rc = lib.rsfa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, H, S, D,
+                          _strides(q, k, v, o), int(causal), scale, 128, 128, _capi.RSFA_DTYPE_F16, stream)
+        assert rc == _capi.RSFA_OK, _capi.strerror(rc)
+        return o, lse
+
+    def noalloc():
+        o = torch.full_like(q, float("nan"))          # poisoned: every element must be written
+        lse = torch.full((B, H, S), float("nan"), dtype=torch.float32, device=dev)
+        rc = lib.rsfa_fwd_noalloc(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                  B, H, S, D, _strides(q, k, v, o), int(causal), scale,
+                                  _capi.RSFA_DTYPE_F16, stream)
+        assert rc == _capi.RSFA_OK, _capi.strerror(rc)
+        return o, lse
+
+    ref_o, ref_lse = regular()
+    for _ in range(2):                                 # second call reuses the same static scratch
+        o, lse = noalloc()
+        torch.cuda.synchronize()
+        assert torch.isfinite(o.float()).all()
+        assert torch.allclose(o.float(), ref_o.float(), atol=1e-2, rtol=1e-2)
+        assert torch.allclose(lse, ref_lse, atol=2e-3, rtol=2e-3)
+        assert torch.equal(o, ref_o)                   # same kernel, same data: bit-identical
+
+
+def test_noalloc_rejects_what_it_cannot_serve(cuda_device):
+    from ascend_rsfa import _capi
+
+    lib = _capi.load()
+    dev = cuda_device
+    q = torch.zeros(1, 1, 256, 32, dtype=torch.float16, device=dev)
+    o = torch.empty_like(q)
+    rc = lib.rsfa_fwd_noalloc(q.data_ptr(), q.data_ptr(), q.data_ptr(), o.data_ptr(), None, 1, 1, 256, 32,
+                              _strides(q, q, q, o), 0, 0.5, _capi.RSFA_DTYPE_F16, None)
+    assert rc == _capi.RSFA_ERR_UNSUPPORTED            # D = 32 has no scratch-using kernel
+    q = torch.zeros(1, 1, 256, 64, dtype=torch.float16, device=dev)
+    o = torch.empty_like(q)
+    st = _strides(q, q, q, o)
+    # more work items than the 32-bit counter in the static block can hand out
+    rc = lib.rsfa_fwd_noalloc(q.data_ptr(), q.data_ptr(), q.data_ptr(), o.data_ptr(), None, 1 << 15, 1 << 15,
+                              512, 64, st, 0, 0.5, _capi.RSFA_DTYPE_F16, None)
+    assert rc == _capi.RSFA_ERR_TOO_LARGE
+    assert "scratch" in _capi.strerror(rc)
+    rc = lib.rsfa_fwd_noalloc(None, q.data_ptr(), q.data_ptr(), o.data_ptr(), None, 1, 1, 256, 64, st, 0, 0.5,
+                              _capi.RSFA_DTYPE_F16, None)
+    assert rc == _capi.RSFA_ERR_INVALID_ARGUMENT
