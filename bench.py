@@ -35,6 +35,9 @@ sys.path.insert(0, os.path.join(ROOT, "ascend-rsfa_b200"))
 import torch
 
 METRIC = "attention fwd TFLOP/s (whole job; causal FLOPs counted as half)"
+# DRAM bytes (read + write) per (batch, head) of S=2048, D=128 from the ncu capture summarised in
+# profiles/fwd_tcgen05_d128_s2048_ncu_full.md (244.9 MB for 128 heads); traffic is proportional to heads.
+NCU_DRAM_BYTES_PER_HEAD_S2048_D128 = 244.9e6 / 128
 FALLBACK_PEAK_TFLOPS = 1590.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 
 
@@ -293,7 +296,10 @@ def main():
             "other_mask": {"causal": (not main_causal), "tflops": other_val, "ms_per_step": other_ms,
                            "pct_of_measured_burst": other_val / world / peaks["burst"]},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["burst"], "unit": "TFLOP/s",
-                         "frac": per_gpu / peaks["burst"], "traffic": None,
+                         "frac": per_gpu / peaks["burst"],
+                         "traffic": (NCU_DRAM_BYTES_PER_HEAD_S2048_D128 * n_local if (S, D) == (2048, 128) else None),
+                         "traffic_note": "scaled from an ncu capture of 128 heads of this shape; algorithmic bytes %.3e"
+                                         % (4.0 * n_local * S * D * 2),
                          "peak_source": peaks["source"] + " cuBLAS bf16 burst; sustained %.1f" % peaks["sustained"],
                          "frac_of_sustained": (per_gpu / peaks["sustained"]) if peaks["sustained"] else None},
             "clocks": clocks.summary(),
