@@ -33,6 +33,9 @@ struct FwdParams {
 cudaError_t launch_fwd_generic(const FwdParams& p, cudaStream_t stream, long long* launches);
 cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t stream,
                                long long* launches);
+// The D = 256 member of the tcgen05 family (reached through launch_fwd_tcgen05).
+cudaError_t launch_fwd_tcgen05_d256(const FwdParams& p, int sm_count, cudaStream_t stream,
+                                    long long* launches);
 // Adds to the process-wide kernel-launch counter behind rsfa_launch_count().
 void count_launches(long long n);
 // True when the tcgen05 kernel is instantiated for this head dimension.

@@ -89,7 +89,7 @@ int choose_path(int S, int D, float sm_scale) {
 void tile_of_path(int path, int D, int* bm, int* bn) {
   if (path == RSFA_PATH_TCGEN05) {
     *bm = 128;
-    *bn = 128;
+    *bn = (D >= 256) ? 64 : 128;
   } else {
     *bm = 64;
     *bn = (D >= 256) ? 32 : 64;

@@ -1,0 +1,147 @@
+// Pieces shared by the tcgen05 attention kernels: wait tags, debug trace hooks, packed-math
+// helpers, register re-budgeting and the host-side TMA map construction.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace rsfa {
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+// Wait-site tags (reported in the status word when a wait runs out).
+enum : int {
+  kTagQEmpty = 1, kTagKvEmpty, kTagQFull, kTagKvFull, kTagPFull, kTagSFull, kTagOFull, kTagSched
+};
+
+// Debug builds (-DRSFA_TRACE) log (clock, code) pairs per role for CTA 0; the product build
+// compiles this away.
+#ifdef RSFA_TRACE
+constexpr int kTraceCap = 4096;
+#define RSFA_TRACE_DECL(role_) \
+  unsigned long long* trace_buf = (p.trace != nullptr && blockIdx.x == 0) ? p.trace + (role_) * 2 * kTraceCap : nullptr; \
+  int trace_n = 0
+#define RSFA_TRACE_EV(code_)                                         \
+  do {                                                               \
+    if (trace_buf != nullptr && trace_n < kTraceCap) {               \
+      trace_buf[2 * trace_n] = static_cast<unsigned long long>(clock64()); \
+      trace_buf[2 * trace_n + 1] = static_cast<unsigned long long>(code_); \
+      ++trace_n;                                                     \
+    }                                                                \
+  } while (0)
+#else
+#define RSFA_TRACE_DECL(role_) do {} while (0)
+#define RSFA_TRACE_EV(code_) do {} while (0)
+#endif
+
+struct TmaMaps {
+  CUtensorMap q, k, v;
+};
+
+struct SchedInfo {
+  int total_items;
+  int items_per_head;  // 256-row blocks per head
+};
+
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (kBf16) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  } else {
+    __half2 t = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// Two fp32 lanes in one 64-bit register: Blackwell's packed FFMA2 / FADD2 halve the issue slots
+// of the scale-and-subtract and of the row sum.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// Register budgets per warpgroup after the common set-up (launch allocates 168 each):
+// 2 x 128 x 208 + 128 x 80 = 63488 of 65536, so the increase never waits on an exact fit.
+constexpr int kRegsSoftmax = 208;
+constexpr int kRegsOther = 80;
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// [B,H,S,D] tensor, 16-bit elements, as a 4-D map (D, S, H, B) with boxes of 64 x `box_rows`.
+bool make_map(CUtensorMap* map, const void* base, const FwdParams& p, const int64_t* st, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(p.D), static_cast<cuuint64_t>(p.S),
+                              static_cast<cuuint64_t>(p.H), static_cast<cuuint64_t>(p.B)};
+  // A dimension of extent 1 may carry any stride; keep the encoder happy with a legal one.
+  auto stride_bytes = [&](int64_t s, int64_t fallback) {
+    return static_cast<cuuint64_t>((s > 0 ? s : fallback) * 2);
+  };
+  const cuuint64_t strides[3] = {stride_bytes(st[2], p.D), stride_bytes(st[1], static_cast<int64_t>(p.S) * p.D),
+                                 stride_bytes(st[0], static_cast<int64_t>(p.H) * p.S * p.D)};
+  const cuuint32_t box[4] = {64u, static_cast<cuuint32_t>(box_rows), 1u, 1u};
+  const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  const CUresult r = enc(map, p.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+}  // namespace rsfa

@@ -93,8 +93,8 @@ RSFA_API int rsfa_fwd_host(const void* q_host, const void* k_host, const void* v
  * process exits) and calls no cudaMalloc, cudaFree or other allocating routine.
  *
  * Arguments as rsfa_fwd, without block_m / block_n (the kernel has one tile).  Limits: only
- * shapes the tcgen05 kernel is built for (D in {64, 128}, sm_scale > 0) -> otherwise
- * RSFA_ERR_UNSUPPORTED; at most 2^30 work items (B * H * ceil(S / 256)), because the queue counter
+ * shapes the tcgen05 kernels are built for (D in {64, 128, 256}, sm_scale > 0) -> otherwise
+ * RSFA_ERR_UNSUPPORTED; at most 2^30 work items (B * H * ceil(S / 256), or ceil(S / 128) at D = 256), because the queue counter
  * is a single 32-bit word of the block -> otherwise RSFA_ERR_TOO_LARGE.
  *
  * The first call on a device looks up the device address of the static block (one

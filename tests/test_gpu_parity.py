@@ -96,7 +96,7 @@ def test_every_head_dim(fa, cuda_device, D, causal):
 
 
 @pytest.mark.parametrize("S", [1, 7, 63, 65, 127, 129, 255, 257, 300, 511, 640, 1000])
-@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("D", [64, 128, 256])
 @pytest.mark.parametrize("causal", [False, True])
 def test_ragged_sequence_lengths(fa, cuda_device, S, D, causal):
     q, k, v = make_inputs(1, 2, S, D, seed=S)
@@ -108,7 +108,7 @@ def test_ragged_sequence_lengths(fa, cuda_device, S, D, causal):
 def test_both_kernel_families_agree(fa, cuda_device, path, causal):
     fa.set_option("force_path", path)
     try:
-        for S, D in [(128, 64), (128, 128), (96, 64), (768, 128), (1536, 64)]:
+        for S, D in [(128, 64), (128, 128), (96, 64), (768, 128), (1536, 64), (320, 256)]:
             q, k, v = make_inputs(2, 2, S, D, seed=9)
             check(fa, q, k, v, causal, 0.3, 128, 128, cuda_device)
     finally:
@@ -137,6 +137,18 @@ def test_wide_logits_online_softmax_stability(fa, cuda_device):
     k2 = torch.gather(k, 2, order[..., None].expand_as(k))
     q2 = k2.flip(2).contiguous()
     check(fa, q2, k2, v, False, 1.0, 128, 128, cuda_device)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_head_dim_256_shapes(fa, cuda_device, causal):
+    # cfg3's per-head shape (S=1024, D=256, sm_scale=1/16) on a few heads, plus forced rescales
+    q, k, v = make_inputs(2, 3, 1024, 256, seed=12)
+    m = check(fa, q, k, v, causal, 1.0 / 16.0, 128, 64, cuda_device)
+    assert m["max_abs"] < 4e-3
+    q, k, v = make_inputs(1, 2, 704, 256, seed=13)
+    check(fa, q, k, v, causal, 1.0, 64, 64, cuda_device)      # peaked rows: the running max keeps moving
+    q, k, v = make_inputs(1, 1, 2048, 256, seed=14, std=0.5)
+    check(fa, q, k, v, causal, 0.5, 64, 256, cuda_device)
 
 
 def test_strided_inputs_and_views(fa, cuda_device):
