@@ -55,6 +55,10 @@ constexpr int kNumThreads = 384;  // 3 warpgroups: softmax 0, softmax 1, {TMA, M
 constexpr int kTmaWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kTmemCols = 512;
+#ifndef RSFA_POLY_OF8
+#define RSFA_POLY_OF8 0
+#endif
+constexpr int kPolyOf8 = RSFA_POLY_OF8;  // pairs out of every 8 whose exp2 runs on the FMA pipe
 
 template <int D>
 struct Cfg {
@@ -221,7 +225,14 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
     }
   } else if (warp == kMmaWarp) {
     // ============================================================== MMA issuer
-    if (lane == 0) {
+    {
+      // Every lane runs this role with identical control flow; only the tcgen05 instructions are
+      // issued by one elected lane.
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+      auto wait_all = [&](uint32_t bar, uint32_t parity, int tag) -> bool {
+        const bool r = mbar_wait(bar, parity, abort_flag, wait_ns, tag);
+        return __all_sync(0xffffffffu, r) != 0;
+      };
       constexpr uint32_t idesc_qk = make_idesc_f16(kTileM, kTileN, kBf16, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(kTileM, D, kBf16, false, true);
       RSFA_TRACE_DECL(2);
@@ -233,10 +244,11 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       bool ok = true;
       while (ok) {
         const int slot = item_count & 1;
-        ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
+        ok = wait_all(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, kTagSched);
         if (!ok) break;
-        const int item = sched_ring[slot];
-        mbar_arrive(bar_sched_empty0 + 8u * slot);
+        const int item = __shfl_sync(0xffffffffu, sched_ring[slot], 0);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sched_empty0 + 8u * slot);
         if (item >= sched.total_items) break;
         int bh, row0;
         decode(item, bh, row0);
@@ -255,7 +267,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t off_q = ((ks >> 2) * C::kQBoxBytes + (ks & 3) * 32) >> 4;
             const uint32_t off_k = ((ks >> 2) * C::kKvBoxBytes + (ks & 3) * 32) >> 4;
-            umma_ss(tmem_base + C::kColS(t), qd + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
+            umma_ss_elect(tmem_u + C::kColS(t), qd + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
           }
         };
         // O_t (+)= P_t V : A = P_t in TMEM (16 keys = 8 columns per step), B = V MN-major:
@@ -264,17 +276,16 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           const uint64_t vd = desc_v0 + static_cast<uint64_t>((vslot * C::kKvTileBytes) >> 4);
 #pragma unroll
           for (int ks = ks_begin; ks < ks_end; ++ks) {
-            umma_ts(tmem_base + C::kColO(t), tmem_base + C::kColS(t) + ks * 8, vd + ((ks * 2048) >> 4),
+            umma_ts_elect(tmem_u + C::kColO(t), tmem_u + C::kColS(t) + ks * 8, vd + ((ks * 2048) >> 4),
                     idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
           }
         };
         auto wait_kv = [&](uint32_t idx) -> bool {
-          return mbar_wait(bar_kv_full(idx % C::kStages), (idx / C::kStages) & 1, abort_flag, wait_ns,
-                           kTagKvFull);
+          return wait_all(bar_kv_full(idx % C::kStages), (idx / C::kStages) & 1, kTagKvFull);
         };
 
         for (int t = 0; ok && t < kNT; ++t)
-          ok = mbar_wait(bar_q_full(t), item_count & 1, abort_flag, wait_ns, kTagQFull);
+          ok = wait_all(bar_q_full(t), item_count & 1, kTagQFull);
         if (!ok) break;
         const uint32_t base = kv_count;  // K_j at base + 2j, V_j at base + 2j + 1
         if (nmax > 0) {
@@ -284,13 +295,13 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           for (int t = 0; t < kNT; ++t) {
             if (n[t] > 0) {
               issue_qk(t, base % C::kStages);
-              umma_commit(bar_s_full(t));
+              umma_commit_elect(bar_s_full(t));
             }
             // Q_t is dead once its last QK^T MMA has run: release it so the next item's Q load
             // overlaps the rest of this item.
-            if (n[t] <= 1) umma_commit(bar_q_empty(t));
+            if (n[t] <= 1) umma_commit_elect(bar_q_empty(t));
           }
-          umma_commit(bar_kv_empty(base % C::kStages));
+          umma_commit_elect(bar_kv_empty(base % C::kStages));
         }
         for (int j = 0; ok && j < nmax; ++j) {
           const uint32_t vidx = base + 2 * j + 1;
@@ -301,20 +312,20 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           bool k_ready = false;
           for (int t = 0; ok && t < kNT; ++t) {
             if (j < n[t]) {
-              ok = mbar_wait(bar_p_full(t, 0), p_count[t] & 1, abort_flag, wait_ns, kTagPFull);
+              ok = wait_all(bar_p_full(t, 0), p_count[t] & 1, kTagPFull);
               if (!ok) break;
               tc_fence_after_sync();
               RSFA_TRACE_EV(0x1000 + (t << 8) + j);   // P half 0 seen
               issue_pv(t, vidx % C::kStages, j > 0, 0, kTileN / 32);
               RSFA_TRACE_EV(0x2000 + (t << 8) + j);   // PV half 0 issued
-              ok = mbar_wait(bar_p_full(t, 1), p_count[t] & 1, abort_flag, wait_ns, kTagPFull);
+              ok = wait_all(bar_p_full(t, 1), p_count[t] & 1, kTagPFull);
               if (!ok) break;
               ++p_count[t];
               tc_fence_after_sync();
               RSFA_TRACE_EV(0x3000 + (t << 8) + j);   // P half 1 seen
               issue_pv(t, vidx % C::kStages, true, kTileN / 32, kTileN / 16);
               RSFA_TRACE_EV(0x4000 + (t << 8) + j);   // PV half 1 issued
-              if (j == n[t] - 1) umma_commit(bar_o_full(t));
+              if (j == n[t] - 1) umma_commit_elect(bar_o_full(t));
             }
             if (j + 1 < n[t]) {
               if (!k_ready) {
@@ -324,19 +335,19 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
                 k_ready = true;
               }
               issue_qk(t, kidx % C::kStages);
-              umma_commit(bar_s_full(t));
+              umma_commit_elect(bar_s_full(t));
               RSFA_TRACE_EV(0x5000 + (t << 8) + j);   // QK(j+1) issued
-              if (j + 2 == n[t]) umma_commit(bar_q_empty(t));
+              if (j + 2 == n[t]) umma_commit_elect(bar_q_empty(t));
             }
           }
           if (!ok) break;
-          umma_commit(bar_kv_empty(vidx % C::kStages));
+          umma_commit_elect(bar_kv_empty(vidx % C::kStages));
           if (j + 1 < nmax) {
             if (!k_ready) {  // tile loaded for a Q tile that did not need it: still consume it
               ok = wait_kv(kidx);
               if (!ok) break;
             }
-            umma_commit(bar_kv_empty(kidx % C::kStages));
+            umma_commit_elect(bar_kv_empty(kidx % C::kStages));
           }
         }
         if (!ok) break;
@@ -476,10 +487,26 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           uint32_t pk[16];
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
-            float x0, x1, x2, x3;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3])), scale2, neg_m2), x2, x3);
-            const float e0 = ex2(x0), e1 = ex2(x1), e2 = ex2(x2), e3 = ex2(x3);
+            const uint64_t xa = fma_f32x2(pack_f32x2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2);
+            const uint64_t xb = fma_f32x2(pack_f32x2(__uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3])), scale2, neg_m2);
+            float e0, e1, e2, e3;
+            // kPolyOf8 of every 8 pairs go to the FMA-pipe polynomial, the rest to the MUFU
+            if (((c >> 1) & 7) < kPolyOf8) {
+              exp2_poly_x2(xa, e0, e1);
+            } else {
+              float x0, x1;
+              unpack_f32x2(xa, x0, x1);
+              e0 = ex2(x0);
+              e1 = ex2(x1);
+            }
+            if ((((c >> 1) + 1) & 7) < kPolyOf8) {
+              exp2_poly_x2(xb, e2, e3);
+            } else {
+              float x2, x3;
+              unpack_f32x2(xb, x2, x3);
+              e2 = ex2(x2);
+              e3 = ex2(x3);
+            }
             sum_a = add_f32x2(sum_a, pack_f32x2(e0, e1));
             sum_b = add_f32x2(sum_b, pack_f32x2(e2, e3));
             pk[c >> 1] = pack2<kBf16>(e0, e1);

@@ -160,7 +160,14 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
     }
   } else if (warp == kMmaWarp256) {
     // ============================================================== MMA issuer
-    if (lane == 0) {
+    {
+      // Every lane runs this role with identical control flow; only the tcgen05 instructions are
+      // issued by one elected lane.
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+      auto wait_all = [&](uint32_t bar, uint32_t parity, int tag) -> bool {
+        const bool r = mbar_wait(bar, parity, abort_flag, wait_ns, tag);
+        return __all_sync(0xffffffffu, r) != 0;
+      };
       constexpr uint32_t idesc_qk = make_idesc_f16(kRows, kKeys, kBf16, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(kRows, kD, kBf16, false, true);
       const uint64_t desc_q0 = make_smem_desc_sw128(sQ, 16, 1024);
@@ -171,10 +178,11 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
       bool ok = true;
       while (ok) {
         const int slot = item_count & 1;
-        ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
+        ok = wait_all(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, kTagSched);
         if (!ok) break;
-        const int item = sched_ring[slot];
-        mbar_arrive(bar_sched_empty0 + 8u * slot);
+        const int item = __shfl_sync(0xffffffffu, sched_ring[slot], 0);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sched_empty0 + 8u * slot);
         if (item >= sched.total_items) break;
         int bh, row0;
         decode(item, bh, row0);
@@ -188,7 +196,7 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
           for (int ks = 0; ks < kD / 16; ++ks) {
             const uint32_t off_q = ((ks >> 2) * kQBoxBytes256 + (ks & 3) * 32) >> 4;
             const uint32_t off_k = ((ks >> 2) * kKvBoxBytes256 + (ks & 3) * 32) >> 4;
-            umma_ss(tmem_base + kColS256 + 64 * buf, desc_q0 + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
+            umma_ss_elect(tmem_u + kColS256 + 64 * buf, desc_q0 + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
           }
         };
         // O (+)= P V: A = P in TMEM (8 columns per 16 keys), B = V MN-major, N = 256 spans the four
@@ -197,15 +205,15 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
           const uint64_t vd = desc_v0 + static_cast<uint64_t>((vslot * kKvBytes256) >> 4);
 #pragma unroll
           for (int ks = 0; ks < kKeys / 16; ++ks) {
-            umma_ts(tmem_base + kColO256, tmem_base + kColS256 + 64 * buf + ks * 8, vd + ((ks * 2048) >> 4),
+            umma_ts_elect(tmem_u + kColO256, tmem_u + kColS256 + 64 * buf + ks * 8, vd + ((ks * 2048) >> 4),
                     idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
           }
         };
         auto wait_kv = [&](uint32_t idx) -> bool {
-          return mbar_wait(bar_kv_full(idx % kStages256), (idx / kStages256) & 1, abort_flag, wait_ns, kTagKvFull);
+          return wait_all(bar_kv_full(idx % kStages256), (idx / kStages256) & 1, kTagKvFull);
         };
 
-        ok = mbar_wait(bar_q_full, item_count & 1, abort_flag, wait_ns, kTagQFull);
+        ok = wait_all(bar_q_full, item_count & 1, kTagQFull);
         if (!ok) break;
         uint32_t idx = kv_count;       // next ring entry to consume
         // prologue: S[0] = Q K_0^T, S[1] = Q K_1^T
@@ -214,33 +222,33 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
           if (!ok) break;
           tc_fence_after_sync();
           issue_qk(j, idx % kStages256);
-          umma_commit(bar_s_full(j));
-          umma_commit(bar_kv_empty(idx % kStages256));
+          umma_commit_elect(bar_s_full(j));
+          umma_commit_elect(bar_kv_empty(idx % kStages256));
           ++idx;
         }
         if (!ok) break;
-        if (n <= 2) umma_commit(bar_q_empty);   // Q is dead after its last QK^T
+        if (n <= 2) umma_commit_elect(bar_q_empty);   // Q is dead after its last QK^T
         for (int j = 0; ok && j < n; ++j) {
           const int buf = j & 1;
           ok = wait_kv(idx);                     // V_j
           if (!ok) break;
-          ok = mbar_wait(bar_p_full(buf), p_count[buf] & 1, abort_flag, wait_ns, kTagPFull);
+          ok = wait_all(bar_p_full(buf), p_count[buf] & 1, kTagPFull);
           if (!ok) break;
           ++p_count[buf];
           tc_fence_after_sync();
           issue_pv(buf, idx % kStages256, j > 0);
-          umma_commit(bar_pv_done);
-          umma_commit(bar_kv_empty(idx % kStages256));
-          if (j == n - 1) umma_commit(bar_o_full);
+          umma_commit_elect(bar_pv_done);
+          umma_commit_elect(bar_kv_empty(idx % kStages256));
+          if (j == n - 1) umma_commit_elect(bar_o_full);
           ++idx;
           if (j + 2 < n) {
             ok = wait_kv(idx);                   // K_{j+2}
             if (!ok) break;
             tc_fence_after_sync();
             issue_qk(buf, idx % kStages256);     // S[buf] is free: PV_j above consumed P_j in order
-            umma_commit(bar_s_full(buf));
-            umma_commit(bar_kv_empty(idx % kStages256));
-            if (j + 3 == n) umma_commit(bar_q_empty);
+            umma_commit_elect(bar_s_full(buf));
+            umma_commit_elect(bar_kv_empty(idx % kStages256));
+            if (j + 3 == n) umma_commit_elect(bar_q_empty);
             ++idx;
           }
         }

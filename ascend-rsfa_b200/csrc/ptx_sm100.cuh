@@ -155,6 +155,34 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       : "memory");
 }
 
+
+// One lane of a converged warp.  The MMA warp keeps its control flow and operand arithmetic
+// warp-uniform (so descriptors live in uniform registers) and elects a lane only for the
+// instruction itself; with a full mask the elected lane is the same every time, which is what
+// lets tcgen05.commit track the MMAs issued before it.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+__device__ __forceinline__ void umma_ss_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  if (elect_one()) umma_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+}
+__device__ __forceinline__ void umma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  if (elect_one()) umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+}
+__device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
+  if (elect_one()) umma_commit(bar);
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle (the layout TMA writes with
 // CU_TENSOR_MAP_SWIZZLE_128B: rows of 128 bytes, 8-row atoms of 1024 bytes).
 //   bits  0..13  start address >> 4        bits 16..29  leading byte offset >> 4
