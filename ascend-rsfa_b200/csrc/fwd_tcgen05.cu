@@ -483,8 +483,11 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         const float neg_m = -m_used * scale_log2;
         const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
         uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
-        auto exp_pack_store = [&](uint32_t (&sv)[32], int chunk) {
-          uint32_t pk[16];
+        // exp2, row sum and 16-bit packing of 32 scores into pk[base .. base+16).  The packed
+        // values of one half (64 keys) are collected first and stored with a single tcgen05.st:
+        // a store issued per 32 scores would make the next chunk's arithmetic wait on it, because
+        // the registers it reads cannot be overwritten until the (slow) TMEM store has taken them.
+        auto exp_pack = [&](uint32_t (&sv)[32], uint32_t (&pk)[32], int base) {
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
             const uint64_t xa = fma_f32x2(pack_f32x2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2);
@@ -509,27 +512,36 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
             }
             sum_a = add_f32x2(sum_a, pack_f32x2(e0, e1));
             sum_b = add_f32x2(sum_b, pack_f32x2(e2, e3));
-            pk[c >> 1] = pack2<kBf16>(e0, e1);
-            pk[(c >> 1) + 1] = pack2<kBf16>(e2, e3);
+            pk[base + (c >> 1)] = pack2<kBf16>(e0, e1);
+            pk[base + (c >> 1) + 1] = pack2<kBf16>(e2, e3);
           }
-          tmem_st_x16(tS + chunk * 16, pk);
         };
-        exp_pack_store(s0, 0);
-        exp_pack_store(s1, 1);
-        tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(bar_p_full(t, 0));
-        RSFA_TRACE_EV(0x4000 + j);   // half 0 handed over
-        exp_pack_store(s2, 2);
-        exp_pack_store(s3, 3);
         {
-          float a0, a1;
-          unpack_f32x2(add_f32x2(sum_a, sum_b), a0, a1);
-          l += a0 + a1;
+          uint32_t pk[32];
+          exp_pack(s0, pk, 0);
+          exp_pack(s1, pk, 16);
+          RSFA_TRACE_EV(0xb000);   // half 0 computed
+          tmem_st_x32(tS, pk);
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(bar_p_full(t, 0));
+          RSFA_TRACE_EV(0x4000 + j);   // half 0 handed over
         }
-        tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(bar_p_full(t, 1));
+        {
+          uint32_t pk[32];
+          exp_pack(s2, pk, 0);
+          exp_pack(s3, pk, 16);
+          RSFA_TRACE_EV(0xb001);   // half 1 computed
+          tmem_st_x32(tS + 32, pk);
+          {
+            float a0, a1;
+            unpack_f32x2(add_f32x2(sum_a, sum_b), a0, a1);
+            l += a0 + a1;
+          }
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(bar_p_full(t, 1));
+        }
         RSFA_TRACE_EV(0x5000 + j);   // half 1 handed over
       }
       if (!ok) break;

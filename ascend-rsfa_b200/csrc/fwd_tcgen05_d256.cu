@@ -360,8 +360,8 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
         const float neg_m = -m_used * scale_log2;
         const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
         uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
-        auto exp_pack_store = [&](uint32_t (&sv)[32], int chunk) {
-          uint32_t pk[16];
+        uint32_t pk[32];   // all 64 keys are packed first, then stored with one tcgen05.st
+        auto exp_pack = [&](uint32_t (&sv)[32], int base) {
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
             float x0, x1, x2, x3;
@@ -370,13 +370,13 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
             const float e0 = ex2(x0), e1 = ex2(x1), e2 = ex2(x2), e3 = ex2(x3);
             sum_a = add_f32x2(sum_a, pack_f32x2(e0, e1));
             sum_b = add_f32x2(sum_b, pack_f32x2(e2, e3));
-            pk[c >> 1] = pack2<kBf16>(e0, e1);
-            pk[(c >> 1) + 1] = pack2<kBf16>(e2, e3);
+            pk[base + (c >> 1)] = pack2<kBf16>(e0, e1);
+            pk[base + (c >> 1) + 1] = pack2<kBf16>(e2, e3);
           }
-          tmem_st_x16(tS + chunk * 16, pk);
         };
-        exp_pack_store(s0, 0);
-        exp_pack_store(s1, 1);
+        exp_pack(s0, 0);
+        exp_pack(s1, 16);
+        tmem_st_x32(tS, pk);
         {
           float a0, a1;
           unpack_f32x2(add_f32x2(sum_a, sum_b), a0, a1);

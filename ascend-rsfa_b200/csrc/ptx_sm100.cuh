@@ -58,16 +58,50 @@ enum : int {
   kStatusWaitExpired = 1,  // a bounded wait ran out; low bits say which role
 };
 
+// try_wait with an explicit suspend-time hint: the hardware may park the thread for up to
+// `hint_ns` nanoseconds (waking it when the phase completes), so a waiting warp does not take
+// issue slots from the warps that are computing on the same scheduler.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
+#ifndef RSFA_WAIT_MODE
+#define RSFA_WAIT_MODE 1   // 0: bare try_wait spin, 1: try_wait with suspend hint, 2: spin + nanosleep back-off
+#endif
+#ifndef RSFA_WAIT_HINT_NS
+#define RSFA_WAIT_HINT_NS 20000
+#endif
+
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by all roles
 // of the CTA: the first role whose wait runs out sets it, every other role sees
 // it at its next poll and leaves as well.  Returns false when the caller must
 // stop.  `tag` identifies the waiting site in the status word.
 __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                            uint64_t limit_ns, int tag) {
+                                               uint64_t limit_ns, int tag) {
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0xffu) == 0) {
+  while (true) {
+#if RSFA_WAIT_MODE == 1
+    if (mbar_try_wait_hint(bar, parity, RSFA_WAIT_HINT_NS)) return true;
+    constexpr uint32_t kCheckMask = 0x3u;
+#else
+    if (mbar_try_wait(bar, parity)) return true;
+    constexpr uint32_t kCheckMask = 0xffu;
+#if RSFA_WAIT_MODE == 2
+    __nanosleep(64);
+#endif
+#endif
+    if ((++spins & kCheckMask) == 0) {
       if (*abort_flag != 0) return false;
       if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = (kStatusWaitExpired << 16) | (tag & 0xffff);
@@ -75,7 +109,6 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, vo
       }
     }
   }
-  return true;
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           uint64_t limit_ns, int tag) {
