@@ -624,7 +624,12 @@ bool tcgen05_supports(int S, int D, float sm_scale) {
   return (D == 64 || D == 128 || D == 256) && S >= 1 && sm_scale > 0.f;
 }
 
+static int g_tcgen05_variant = 0;
+void set_tcgen05_variant(int v) { g_tcgen05_variant = v; }
+int get_tcgen05_variant() { return g_tcgen05_variant; }
+
 cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches) {
+  if (g_tcgen05_variant == 1) return launch_fwd_tcgen05_db(p, sm_count, stream, launches);
   if (p.D == 256) return launch_fwd_tcgen05_d256(p, sm_count, stream, launches);
   if (p.D == 128) return p.bf16 ? launch_one<128, true>(p, sm_count, stream, launches)
                                 : launch_one<128, false>(p, sm_count, stream, launches);

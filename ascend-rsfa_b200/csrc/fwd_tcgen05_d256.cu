@@ -173,6 +173,7 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
       const uint64_t desc_q0 = make_smem_desc_sw128(sQ, 16, 1024);
       const uint64_t desc_k0 = make_smem_desc_sw128(sKV, 16, 1024);
       const uint64_t desc_v0 = make_smem_desc_sw128(sKV, kKvBoxBytes256, 1024);
+      RSFA_TRACE_DECL(2);
       uint32_t kv_count = 0, item_count = 0;
       uint32_t p_count[2] = {0, 0};
       bool ok = true;
@@ -232,11 +233,14 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
           const int buf = j & 1;
           ok = wait_kv(idx);                     // V_j
           if (!ok) break;
+          RSFA_TRACE_EV(0x6000 + j);   // V present
           ok = wait_all(bar_p_full(buf), p_count[buf] & 1, kTagPFull);
           if (!ok) break;
           ++p_count[buf];
           tc_fence_after_sync();
+          RSFA_TRACE_EV(0x1000 + j);   // P seen
           issue_pv(buf, idx % kStages256, j > 0);
+          RSFA_TRACE_EV(0x2000 + j);   // PV issued
           umma_commit_elect(bar_pv_done);
           umma_commit_elect(bar_kv_empty(idx % kStages256));
           if (j == n - 1) umma_commit_elect(bar_o_full);
@@ -245,7 +249,9 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
             ok = wait_kv(idx);                   // K_{j+2}
             if (!ok) break;
             tc_fence_after_sync();
+            RSFA_TRACE_EV(0x3000 + j);   // K(j+2) present
             issue_qk(buf, idx % kStages256);     // S[buf] is free: PV_j above consumed P_j in order
+            RSFA_TRACE_EV(0x5000 + j);   // QK(j+2) issued
             umma_commit_elect(bar_s_full(buf));
             umma_commit_elect(bar_kv_empty(idx % kStages256));
             if (j + 3 == n) umma_commit_elect(bar_q_empty);
@@ -266,6 +272,10 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
     uint32_t item_count = 0, o_count = 0, pv_count = 0;
     uint32_t s_count[2] = {0, 0};
     bool ok = true;
+#ifdef RSFA_TRACE
+    unsigned long long* trace_buf = (p.trace != nullptr && blockIdx.x == 0 && warp == 0 && lane == 0) ? p.trace : nullptr;
+    int trace_n = 0;
+#endif
     while (ok) {
       const int slot = item_count & 1;
       ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
@@ -291,6 +301,7 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
         if (!ok) break;
         ++s_count[buf];
         tc_fence_after_sync();
+        RSFA_TRACE_EV(0x1000 + j);   // S seen
 
         uint32_t s0[32], s1[32];
         tmem_ld_x32(tS + 0, s0);
@@ -356,6 +367,7 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
           }
         }
 
+        RSFA_TRACE_EV(0x3000 + j);   // max done
         const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
         const float neg_m = -m_used * scale_log2;
         const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
@@ -385,6 +397,7 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(bar_p_full(buf));
+        RSFA_TRACE_EV(0x5000 + j);   // P handed over
       }
       if (!ok) break;
       pv_count += n;
@@ -395,6 +408,7 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
       if (!ok) break;
       ++o_count;
       tc_fence_after_sync();
+      RSFA_TRACE_EV(0x6000);   // O seen
       const float inv_l = 1.f / l;
       const int b = bh / p.H, h = bh - b * p.H;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_stride[0] + h * p.o_stride[1] +
@@ -420,6 +434,7 @@ fwd_tcgen05_d256_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p,
       if (p.lse != nullptr && row < S)
         p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);
       tc_fence_before_sync();
+      RSFA_TRACE_EV(0x7000);   // epilogue done
     }
   }
 

@@ -1,0 +1,540 @@
+// FlashAttention-2 forward for B200 (sm_100a), "double-buffered S" kernel family.
+//
+// Replaces the reference's tiled kernels _attn_fwd / _attn_fwd_inner(_d64_nc) and the causal
+// split _run_causal_split (ascend_rsfa/flash_attention_forward.py:163-541) in one launch.
+//
+// A CTA owns kNT Q tiles of 128 rows of one (batch, head) and sweeps the keys in tiles of 64.
+// Each Q tile has TWO S buffers in tensor memory, so the MMA warp computes S for key tile j+2
+// while the softmax warps are still on tile j+1: the softmax -> PV -> QK^T dependency chain of a
+// single-buffered design is cut, the tensor pipe and the softmax warps each run back to back.
+//   S_t[j & 1] = Q_t K_j^T    D/16 MMAs of 128 x 64 x 16, both operands in shared memory
+//   softmax group t           tcgen05.ld S -> mask (diagonal / ragged tiles) -> row max -> lazy
+//                             rescale -> exp2 -> row sum -> P_j (16-bit) over S_t[j & 1]
+//   O_t += P_j V_j            4 MMAs of 128 x D x 16, A = P_j from TMEM, B = V_j MN-major
+// TMEM columns: S_t[b] at 128 t + 64 b, O_t at 128 kNT + D t (kNT = 2 for D <= 128, 1 for D = 256).
+// Shared memory: Q tiles + a ring of K/V tiles of 64 keys filled by TMA (128-byte swizzle).
+// Roles: warps [0, 4 kNT) softmax (one thread per row), then one TMA warp and one MMA warp.
+// Work items (batch*head, block of 128 kNT rows) come from an atomic queue, head-major, causal
+// blocks heaviest first inside a head.
+#include "tcgen05_common.cuh"
+
+namespace rsfa {
+namespace {
+
+constexpr int kRowsDb = 128;   // rows per Q tile (= TMEM lanes)
+constexpr int kKeysDb = 64;    // keys per K/V tile
+
+template <int D, int NT>
+struct DbCfg {
+  static constexpr int kBoxes = D / 64;
+  static constexpr int kQBoxBytes = kRowsDb * 128;
+  static constexpr int kQTileBytes = kBoxes * kQBoxBytes;
+  static constexpr int kKvBoxBytes = kKeysDb * 128;
+  static constexpr int kKvBytes = kBoxes * kKvBoxBytes;
+  static constexpr int kStages = (D == 256) ? 4 : (D == 128 ? 8 : 12);
+  static constexpr int kThreads = 32 * (4 * NT + 2);
+  static constexpr int kTmaWarp = 4 * NT;
+  static constexpr int kMmaWarp = 4 * NT + 1;
+  // q_full, q_empty, pv_done, o_full per tile; s_full, p_full per (tile, buffer); ring; scheduler
+  static constexpr int kNumBarriers = 4 * NT + 4 * NT + 2 * kStages + 4;
+  static constexpr int kSmemBytes = NT * kQTileBytes + kStages * kKvBytes + 1024 + kNumBarriers * 8 + 64;
+  __host__ __device__ static constexpr int col_s(int t, int b) { return 128 * t + 64 * b; }
+  __host__ __device__ static constexpr int col_o(int t) { return 128 * NT + D * t; }
+};
+
+__device__ __forceinline__ int num_kv_tiles_db(int row0, int S, int causal) {
+  if (row0 >= S) return 0;
+  const int last_key = causal ? min(S, row0 + kRowsDb) : S;  // exclusive
+  return (last_key + kKeysDb - 1) / kKeysDb;
+}
+
+template <int D, int NT, bool kBf16>
+__global__ void __launch_bounds__(DbCfg<D, NT>::kThreads, 1)
+fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, const SchedInfo sched) {
+  using C = DbCfg<D, NT>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = smem_base;
+  const uint32_t sKV = sQ + NT * C::kQTileBytes;
+  const uint32_t sBar = sKV + C::kStages * C::kKvBytes;
+  auto bar_q_full = [&](int t) { return sBar + 8u * t; };
+  auto bar_q_empty = [&](int t) { return sBar + 8u * (NT + t); };
+  auto bar_pv_done = [&](int t) { return sBar + 8u * (2 * NT + t); };   // one completion per key tile
+  auto bar_o_full = [&](int t) { return sBar + 8u * (3 * NT + t); };    // one completion per work item
+  auto bar_s_full = [&](int t, int b) { return sBar + 8u * (4 * NT + 2 * t + b); };
+  auto bar_p_full = [&](int t, int b) { return sBar + 8u * (6 * NT + 2 * t + b); };
+  auto bar_kv_full = [&](int s) { return sBar + 8u * (8 * NT + s); };
+  auto bar_kv_empty = [&](int s) { return sBar + 8u * (8 * NT + C::kStages + s); };
+  const uint32_t bar_sched_full0 = sBar + 8u * (8 * NT + 2 * C::kStages);  // 2 slots
+  const uint32_t bar_sched_empty0 = bar_sched_full0 + 16u;                 // 2 slots
+  const uint32_t misc = sBar + 8u * C::kNumBarriers;
+  uint8_t* misc_ptr = smem_raw + (misc - smem_u32(smem_raw));
+  volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(misc_ptr);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc_ptr + 4);
+  volatile int* sched_ring = reinterpret_cast<volatile int*>(misc_ptr + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint64_t wait_ns = p.wait_limit_ns;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int t = 0; t < NT; ++t) {
+      mbar_init(bar_q_full(t), 1);
+      mbar_init(bar_q_empty(t), 1);
+      mbar_init(bar_pv_done(t), 1);
+      mbar_init(bar_o_full(t), 1);
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(bar_s_full(t, b), 1);
+        mbar_init(bar_p_full(t, b), kRowsDb);
+      }
+    }
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(bar_kv_full(s), 1);
+      mbar_init(bar_kv_empty(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_sched_full0 + 8u * s, 1);
+      mbar_init(bar_sched_empty0 + 8u * s, 1 + 4 * NT);  // MMA warp + one lane per softmax warp
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == C::kMmaWarp) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), 512);
+    tmem_relinquish();
+  }
+  if (warp == C::kTmaWarp && lane == 0) {
+    tma_prefetch_desc(&maps.q);
+    tma_prefetch_desc(&maps.k);
+    tma_prefetch_desc(&maps.v);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  const int S = p.S;
+  const int items_per_head = sched.items_per_head;
+  auto decode = [&](int item, int& bh, int& row0) {
+    bh = item / items_per_head;
+    int blk = item - bh * items_per_head;
+    if (p.causal) blk = items_per_head - 1 - blk;   // heaviest block first inside a head
+    row0 = blk * (NT * kRowsDb);
+  };
+
+  if (warp == C::kTmaWarp) {
+    // ================================================================ producer
+    // Ring order = consumption order of the MMA warp: K_0, K_1, then V_j, K_{j+2} for j = 0, 1, ...
+    if (lane == 0) {
+      RSFA_TRACE_DECL(3);
+      uint32_t kv_count = 0, item_count = 0;
+      bool ok = true;
+      while (ok) {
+        const int slot = item_count & 1;
+        ok = mbar_wait(bar_sched_empty0 + 8u * slot, ((item_count >> 1) & 1) ^ 1, abort_flag, wait_ns, kTagSched);
+        if (!ok) break;
+        const int item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
+        sched_ring[slot] = item;
+        __threadfence_block();
+        mbar_arrive(bar_sched_full0 + 8u * slot);
+        if (item >= sched.total_items) break;
+        int bh, row0;
+        decode(item, bh, row0);
+        const int b = bh / p.H, h = bh - b * p.H;
+        int nmax = 0;
+        for (int t = 0; t < NT; ++t) nmax = max(nmax, num_kv_tiles_db(row0 + t * kRowsDb, S, p.causal));
+        auto load_kv = [&](const CUtensorMap* map, int j) -> bool {
+          const uint32_t s = kv_count % C::kStages;
+          const uint32_t ph = (kv_count / C::kStages) & 1;
+          if (!mbar_wait(bar_kv_empty(s), ph ^ 1, abort_flag, wait_ns, kTagKvEmpty)) return false;
+          RSFA_TRACE_EV(0x200 + j);
+          mbar_arrive_expect_tx(bar_kv_full(s), C::kKvBytes);
+          for (int bx = 0; bx < C::kBoxes; ++bx)
+            tma_load_4d(sKV + s * C::kKvBytes + bx * C::kKvBoxBytes, map, bar_kv_full(s), bx * 64, j * kKeysDb, h, b);
+          ++kv_count;
+          return true;
+        };
+        // K_0 and K_1 before the Q tiles: their slots free up while the previous item drains,
+        // whereas a Q buffer is released only when that item's last QK^T on it has finished.
+        ok = load_kv(&maps.k, 0);
+        if (ok && nmax > 1) ok = load_kv(&maps.k, 1);
+        for (int t = 0; ok && t < NT; ++t) {
+          ok = mbar_wait(bar_q_empty(t), (item_count & 1) ^ 1, abort_flag, wait_ns, kTagQEmpty);
+          if (!ok) break;
+          RSFA_TRACE_EV(0x100 + t);
+          mbar_arrive_expect_tx(bar_q_full(t), C::kQTileBytes);
+          for (int bx = 0; bx < C::kBoxes; ++bx)
+            tma_load_4d(sQ + t * C::kQTileBytes + bx * C::kQBoxBytes, &maps.q, bar_q_full(t), bx * 64,
+                        row0 + t * kRowsDb, h, b);
+        }
+        for (int j = 0; ok && j < nmax; ++j) {
+          ok = load_kv(&maps.v, j);
+          if (ok && j + 2 < nmax) ok = load_kv(&maps.k, j + 2);
+        }
+        ++item_count;
+      }
+    }
+  } else if (warp == C::kMmaWarp) {
+    // ============================================================== MMA issuer
+    // Every lane runs this role with identical control flow (operands stay in uniform registers);
+    // only the tcgen05 instructions are issued by one elected lane.
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+    auto wait_all = [&](uint32_t bar, uint32_t parity, int tag) -> bool {
+      const bool r = mbar_wait(bar, parity, abort_flag, wait_ns, tag);
+      return __all_sync(0xffffffffu, r) != 0;
+    };
+    constexpr uint32_t idesc_qk = make_idesc_f16(kRowsDb, kKeysDb, kBf16, false, false);
+    constexpr uint32_t idesc_pv = make_idesc_f16(kRowsDb, D, kBf16, false, true);
+    RSFA_TRACE_DECL(2);
+    const uint64_t desc_q0 = make_smem_desc_sw128(sQ, 16, 1024);
+    const uint64_t desc_k0 = make_smem_desc_sw128(sKV, 16, 1024);
+    const uint64_t desc_v0 = make_smem_desc_sw128(sKV, C::kKvBoxBytes, 1024);
+    uint32_t kv_count = 0, item_count = 0;
+    uint32_t p_count[NT][2];
+    for (int t = 0; t < NT; ++t) p_count[t][0] = p_count[t][1] = 0;
+    bool ok = true;
+    while (ok) {
+      const int slot = item_count & 1;
+      ok = wait_all(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, kTagSched);
+      if (!ok) break;
+      const int item = __shfl_sync(0xffffffffu, sched_ring[slot], 0);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sched_empty0 + 8u * slot);
+      if (item >= sched.total_items) break;
+      int bh, row0;
+      decode(item, bh, row0);
+      int n[NT];
+      int nmax = 0;
+      for (int t = 0; t < NT; ++t) {
+        n[t] = num_kv_tiles_db(row0 + t * kRowsDb, S, p.causal);
+        nmax = max(nmax, n[t]);
+      }
+      // S_t[buf] = Q_t K^T: K-major operands; 16 elements of D per step = 32 B inside a swizzle
+      // row, four steps per 64-column box.
+      auto issue_qk = [&](int t, int buf, uint32_t kslot) {
+        const uint64_t qd = desc_q0 + static_cast<uint64_t>((t * C::kQTileBytes) >> 4);
+        const uint64_t kd = desc_k0 + static_cast<uint64_t>((kslot * C::kKvBytes) >> 4);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off_q = ((ks >> 2) * C::kQBoxBytes + (ks & 3) * 32) >> 4;
+          const uint32_t off_k = ((ks >> 2) * C::kKvBoxBytes + (ks & 3) * 32) >> 4;
+          umma_ss_elect(tmem_u + C::col_s(t, buf), qd + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
+        }
+      };
+      // O_t (+)= P V: A = P in TMEM (8 columns per 16 keys), B = V MN-major, N = D spans D/64
+      // boxes (kKvBoxBytes apart), 16 keys = two 8-row atoms of 1024 B.
+      auto issue_pv = [&](int t, int buf, uint32_t vslot, bool accumulate) {
+        const uint64_t vd = desc_v0 + static_cast<uint64_t>((vslot * C::kKvBytes) >> 4);
+#pragma unroll
+        for (int ks = 0; ks < kKeysDb / 16; ++ks) {
+          umma_ts_elect(tmem_u + C::col_o(t), tmem_u + C::col_s(t, buf) + ks * 8, vd + ((ks * 2048) >> 4), idesc_pv,
+                        (accumulate || ks > 0) ? 1u : 0u);
+        }
+      };
+      auto wait_kv = [&](uint32_t idx) -> bool {
+        return wait_all(bar_kv_full(idx % C::kStages), (idx / C::kStages) & 1, kTagKvFull);
+      };
+
+      for (int t = 0; ok && t < NT; ++t) ok = wait_all(bar_q_full(t), item_count & 1, kTagQFull);
+      if (!ok) break;
+      uint32_t idx = kv_count;   // next ring entry to consume
+      // prologue: S_t[0] = Q_t K_0^T, S_t[1] = Q_t K_1^T
+      for (int j = 0; ok && j < 2 && j < nmax; ++j) {
+        ok = wait_kv(idx);
+        if (!ok) break;
+        tc_fence_after_sync();
+        for (int t = 0; t < NT; ++t) {
+          if (j < n[t]) {
+            issue_qk(t, j, idx % C::kStages);
+            umma_commit_elect(bar_s_full(t, j));
+          }
+        }
+        umma_commit_elect(bar_kv_empty(idx % C::kStages));
+        ++idx;
+      }
+      if (!ok) break;
+      // a Q tile is dead once its last QK^T has been issued: release it for the next item
+      for (int t = 0; t < NT; ++t)
+        if (n[t] <= 2) umma_commit_elect(bar_q_empty(t));
+      for (int j = 0; ok && j < nmax; ++j) {
+        const int buf = j & 1;
+        const uint32_t vidx = idx;
+        const uint32_t kidx = idx + 1;
+        const bool more_k = (j + 2 < nmax);
+        ok = wait_kv(vidx);   // V_j
+        if (!ok) break;
+        RSFA_TRACE_EV(0x6000 + j);   // V present
+        bool k_ready = false;
+        for (int t = 0; ok && t < NT; ++t) {
+          if (j < n[t]) {
+            ok = wait_all(bar_p_full(t, buf), p_count[t][buf] & 1, kTagPFull);
+            if (!ok) break;
+            ++p_count[t][buf];
+            tc_fence_after_sync();
+            RSFA_TRACE_EV(0x1000 + (t << 8) + j);   // P seen
+            issue_pv(t, buf, vidx % C::kStages, j > 0);
+            umma_commit_elect(bar_pv_done(t));
+            if (j == n[t] - 1) umma_commit_elect(bar_o_full(t));
+            RSFA_TRACE_EV(0x2000 + (t << 8) + j);   // PV issued
+          }
+          if (j + 2 < n[t]) {
+            if (!k_ready) {
+              ok = wait_kv(kidx);   // K_{j+2}
+              if (!ok) break;
+              tc_fence_after_sync();
+              k_ready = true;
+            }
+            issue_qk(t, buf, kidx % C::kStages);   // S_t[buf] is free: PV above consumed P_j in order
+            umma_commit_elect(bar_s_full(t, buf));
+            if (j + 3 == n[t]) umma_commit_elect(bar_q_empty(t));
+            RSFA_TRACE_EV(0x5000 + (t << 8) + j);   // QK(j+2) issued
+          }
+        }
+        if (!ok) break;
+        umma_commit_elect(bar_kv_empty(vidx % C::kStages));
+        ++idx;
+        if (more_k) {
+          if (!k_ready) {
+            ok = wait_kv(kidx);
+            if (!ok) break;
+          }
+          umma_commit_elect(bar_kv_empty(kidx % C::kStages));
+          ++idx;
+        }
+      }
+      if (!ok) break;
+      kv_count = idx;
+      ++item_count;
+    }
+  } else {
+    // ========================================================== softmax groups
+    const int t = warp >> 2;   // Q tile of this group
+    const int row_in_tile = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tO = tmem_base + lane_base + C::col_o(t);
+    const float scale_log2 = p.sm_scale * kLog2e;
+    uint32_t item_count = 0, o_count = 0, pv_count = 0;
+    uint32_t s_count[2] = {0, 0};
+    bool ok = true;
+#ifdef RSFA_TRACE
+    unsigned long long* trace_buf = (p.trace != nullptr && blockIdx.x == 0 && (warp & 3) == 0 && lane == 0)
+                                        ? p.trace + t * 2 * kTraceCap : nullptr;
+    int trace_n = 0;
+#endif
+    while (ok) {
+      const int slot = item_count & 1;
+      ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int item = sched_ring[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sched_empty0 + 8u * slot);
+      if (item >= sched.total_items) break;
+      ++item_count;
+      int bh, row0;
+      decode(item, bh, row0);
+      const int tile_row0 = row0 + t * kRowsDb;
+      const int row = tile_row0 + row_in_tile;
+      const int n = num_kv_tiles_db(tile_row0, S, p.causal);
+      if (n == 0) continue;
+
+      float m_used = -INFINITY;   // reference max, raw score units
+      float l = 0.f;
+      for (int j = 0; j < n; ++j) {
+        const int buf = j & 1;
+        const uint32_t tS = tmem_base + lane_base + C::col_s(t, buf);
+        ok = mbar_wait(bar_s_full(t, buf), s_count[buf] & 1, abort_flag, wait_ns, kTagSFull);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        ++s_count[buf];
+        tc_fence_after_sync();
+        RSFA_TRACE_EV(0x1000 + j);   // S seen
+
+        uint32_t s0[32], s1[32];
+        tmem_ld_x32(tS + 0, s0);
+        tmem_ld_x32(tS + 32, s1);
+        tmem_wait_ld();
+        reg_fence_x32(s0);
+        reg_fence_x32(s1);
+
+        // masked tile: one that crosses the diagonal, or the ragged end of the sequence
+        const int n0 = j * kKeysDb;
+        const bool masked = (n0 + kKeysDb > S) || (p.causal && n0 + kKeysDb > tile_row0 + 1);
+        if (masked) {
+          int limit = S - 1 - n0;   // last visible column of this tile
+          if (p.causal) limit = min(limit, row - n0);
+          const uint32_t ninf = 0xff800000u;
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            if (c > limit) s0[c] = ninf;
+            if (c + 32 > limit) s1[c] = ninf;
+          }
+        }
+        float mb;
+        {
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            mx[0] = max3(mx[0], __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
+            mx[1] = max3(mx[1], __uint_as_float(s0[c + 2]), __uint_as_float(s0[c + 3]));
+            mx[2] = max3(mx[2], __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
+            mx[3] = max3(mx[3], __uint_as_float(s1[c + 2]), __uint_as_float(s1[c + 3]));
+          }
+          mb = fmaxf(max3(mx[0], mx[1], mx[2]), mx[3]);
+        }
+        // With 64-key tiles the upper rows of a Q tile see nothing of the second diagonal tile:
+        // such a row keeps its reference max (moving it towards 0 could underflow l).
+        const bool nothing_visible = (mb == -INFINITY);
+
+        // Lazy rescale: the reference max moves only when the row max grew by more than 2^8 (the
+        // reference's threshold-0 "rescale skipping", :466-487, generalised).
+        float alpha = 1.f;
+        bool grow = false;
+        if (j == 0) {
+          m_used = nothing_visible ? 0.f : mb;
+        } else if (!nothing_visible && (mb - m_used) * scale_log2 > kRescaleThreshold) {
+          alpha = ex2((m_used - mb) * scale_log2);
+          l *= alpha;
+          m_used = mb;
+          grow = true;
+        }
+        if (__any_sync(0xffffffffu, grow)) {
+          // QK^T of this tile was issued before PV of the previous one, so O_t may still be
+          // written: wait for PV_{j-1} (completion number pv_count + j - 1 of this tile).
+          ok = mbar_wait(bar_pv_done(t), (pv_count + j - 1) & 1, abort_flag, wait_ns, kTagOFull);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld_x32(tO + c0, o);
+            tmem_wait_ld();
+            reg_fence_x32(o);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+            tmem_st_x32(tO + c0, o);
+            tmem_wait_st();
+          }
+        }
+        RSFA_TRACE_EV(0x3000 + j);   // max done
+
+        const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
+        const float neg_m = -m_used * scale_log2;
+        const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
+        uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
+        uint32_t pk[32];   // all 64 keys are packed first, then stored with one tcgen05.st
+        auto exp_pack = [&](uint32_t (&sv)[32], int base) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            float x0, x1, x2, x3;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3])), scale2, neg_m2), x2, x3);
+            const float e0 = ex2(x0), e1 = ex2(x1), e2 = ex2(x2), e3 = ex2(x3);
+            sum_a = add_f32x2(sum_a, pack_f32x2(e0, e1));
+            sum_b = add_f32x2(sum_b, pack_f32x2(e2, e3));
+            pk[base + (c >> 1)] = pack2<kBf16>(e0, e1);
+            pk[base + (c >> 1) + 1] = pack2<kBf16>(e2, e3);
+          }
+        };
+        exp_pack(s0, 0);
+        exp_pack(s1, 16);
+        tmem_st_x32(tS, pk);
+        {
+          float a0, a1;
+          unpack_f32x2(add_f32x2(sum_a, sum_b), a0, a1);
+          l += a0 + a1;
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar_p_full(t, buf));
+        RSFA_TRACE_EV(0x5000 + j);   // P handed over
+      }
+      if (!ok) break;
+      pv_count += n;
+
+      // ---- epilogue: O_t / l -> global, lse = m + log l (natural log; :400-404)
+      ok = mbar_wait(bar_o_full(t), o_count & 1, abort_flag, wait_ns, kTagOFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ++o_count;
+      tc_fence_after_sync();
+      RSFA_TRACE_EV(0x6000);   // O seen
+      const float inv_l = 1.f / l;
+      const int b = bh / p.H, h = bh - b * p.H;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_stride[0] + h * p.o_stride[1] +
+                       static_cast<int64_t>(row) * p.o_stride[2];
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t o[32];
+        tmem_ld_x32(tO + c0, o);
+        tmem_wait_ld();
+        reg_fence_x32(o);
+        if (row < S) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint4 v4;
+            v4.x = pack2<kBf16>(__uint_as_float(o[c + 0]) * inv_l, __uint_as_float(o[c + 1]) * inv_l);
+            v4.y = pack2<kBf16>(__uint_as_float(o[c + 2]) * inv_l, __uint_as_float(o[c + 3]) * inv_l);
+            v4.z = pack2<kBf16>(__uint_as_float(o[c + 4]) * inv_l, __uint_as_float(o[c + 5]) * inv_l);
+            v4.w = pack2<kBf16>(__uint_as_float(o[c + 6]) * inv_l, __uint_as_float(o[c + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c0 + c) = v4;
+          }
+        }
+      }
+      if (p.lse != nullptr && row < S)
+        p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);
+      tc_fence_before_sync();
+      RSFA_TRACE_EV(0x7000);   // epilogue done
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag != 0) {
+    // Give copies and MMAs still in flight time to land before shared memory and TMEM go away.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == C::kMmaWarp) tmem_dealloc(tmem_base, 512);
+  if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
+}
+
+template <int D, int NT, bool kBf16>
+cudaError_t launch_db(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches) {
+  using C = DbCfg<D, NT>;
+  TmaMaps maps;
+  if (!make_map(&maps.q, p.q, p, p.q_stride, kRowsDb) || !make_map(&maps.k, p.k, p, p.k_stride, kKeysDb) ||
+      !make_map(&maps.v, p.v, p, p.v_stride, kKeysDb))
+    return cudaErrorInvalidValue;
+  SchedInfo sched;
+  sched.items_per_head = (p.S + NT * kRowsDb - 1) / (NT * kRowsDb);
+  sched.total_items = sched.items_per_head * p.B * p.H;
+  auto kern = fwd_tcgen05_db_kernel<D, NT, kBf16>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  e = cudaMemsetAsync(p.tile_counter, 0, sizeof(unsigned int), stream);
+  if (e != cudaSuccess) return e;
+  const int grid = sched.total_items < sm_count ? sched.total_items : sm_count;
+  kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(maps, p, sched);
+  e = cudaGetLastError();
+  if (e == cudaSuccess) *launches += 1;
+  return e;
+}
+
+}  // namespace
+
+cudaError_t launch_fwd_tcgen05_db(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches) {
+  switch (p.D) {
+    case 64: return p.bf16 ? launch_db<64, 2, true>(p, sm_count, stream, launches) : launch_db<64, 2, false>(p, sm_count, stream, launches);
+    case 128: return p.bf16 ? launch_db<128, 2, true>(p, sm_count, stream, launches) : launch_db<128, 2, false>(p, sm_count, stream, launches);
+    case 256: return p.bf16 ? launch_db<256, 1, true>(p, sm_count, stream, launches) : launch_db<256, 1, false>(p, sm_count, stream, launches);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace rsfa

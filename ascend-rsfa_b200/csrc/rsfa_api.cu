@@ -139,6 +139,11 @@ int rsfa_set_option(const char* name, long long value) {
     return RSFA_OK;
   }
 #endif
+  if (std::strcmp(name, "tcgen05_variant") == 0) {
+    if (value < 0 || value > 1) return RSFA_ERR_INVALID_ARGUMENT;
+    rsfa::set_tcgen05_variant(static_cast<int>(value));
+    return RSFA_OK;
+  }
   if (std::strcmp(name, "host_slab_heads") == 0) {
     if (value < 0) return RSFA_ERR_INVALID_ARGUMENT;
     g_host_slab_heads.store(value);
@@ -152,6 +157,7 @@ long long rsfa_get_option(const char* name) {
   if (std::strcmp(name, "force_path") == 0) return g_force_path.load();
   if (std::strcmp(name, "wait_limit_ms") == 0) return g_wait_limit_ms.load();
   if (std::strcmp(name, "host_slab_heads") == 0) return g_host_slab_heads.load();
+  if (std::strcmp(name, "tcgen05_variant") == 0) return rsfa::get_tcgen05_variant();
   return RSFA_ERR_INVALID_ARGUMENT;
 }
 
