@@ -33,14 +33,11 @@ struct FwdParams {
 cudaError_t launch_fwd_generic(const FwdParams& p, cudaStream_t stream, long long* launches);
 cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t stream,
                                long long* launches);
-// The D = 256 member of the tcgen05 family (reached through launch_fwd_tcgen05).
-cudaError_t launch_fwd_tcgen05_d256(const FwdParams& p, int sm_count, cudaStream_t stream,
-                                    long long* launches);
 // The double-buffered-S family (D = 64, 128, 256), selected by launch_fwd_tcgen05.
 cudaError_t launch_fwd_tcgen05_db(const FwdParams& p, int sm_count, cudaStream_t stream,
                                   long long* launches);
-// Kernel variant of the tcgen05 family: 0 = single-buffered S (two Q tiles ping-pong, 128-key
-// tiles; D = 256: one Q tile), 1 = double-buffered S with 64-key tiles.
+// Kernel variant of the tcgen05 family for D <= 128: 0 = single-buffered S (two Q tiles
+// ping-pong, 128-key tiles), 1 = double-buffered S with 64-key tiles.  D = 256 always uses the latter.
 void set_tcgen05_variant(int v);
 int get_tcgen05_variant();
 // Adds to the process-wide kernel-launch counter behind rsfa_launch_count().

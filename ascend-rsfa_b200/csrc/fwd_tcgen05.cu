@@ -55,10 +55,6 @@ constexpr int kNumThreads = 384;  // 3 warpgroups: softmax 0, softmax 1, {TMA, M
 constexpr int kTmaWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kTmemCols = 512;
-#ifndef RSFA_POLY_OF8
-#define RSFA_POLY_OF8 0
-#endif
-constexpr int kPolyOf8 = RSFA_POLY_OF8;  // pairs out of every 8 whose exp2 runs on the FMA pipe
 
 template <int D>
 struct Cfg {
@@ -492,24 +488,10 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           for (int c = 0; c < 32; c += 4) {
             const uint64_t xa = fma_f32x2(pack_f32x2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2);
             const uint64_t xb = fma_f32x2(pack_f32x2(__uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3])), scale2, neg_m2);
-            float e0, e1, e2, e3;
-            // kPolyOf8 of every 8 pairs go to the FMA-pipe polynomial, the rest to the MUFU
-            if (((c >> 1) & 7) < kPolyOf8) {
-              exp2_poly_x2(xa, e0, e1);
-            } else {
-              float x0, x1;
-              unpack_f32x2(xa, x0, x1);
-              e0 = ex2(x0);
-              e1 = ex2(x1);
-            }
-            if ((((c >> 1) + 1) & 7) < kPolyOf8) {
-              exp2_poly_x2(xb, e2, e3);
-            } else {
-              float x2, x3;
-              unpack_f32x2(xb, x2, x3);
-              e2 = ex2(x2);
-              e3 = ex2(x3);
-            }
+            float x0, x1, x2, x3;
+            unpack_f32x2(xa, x0, x1);
+            unpack_f32x2(xb, x2, x3);
+            const float e0 = ex2(x0), e1 = ex2(x1), e2 = ex2(x2), e3 = ex2(x3);
             sum_a = add_f32x2(sum_a, pack_f32x2(e0, e1));
             sum_b = add_f32x2(sum_b, pack_f32x2(e2, e3));
             pk[base + (c >> 1)] = pack2<kBf16>(e0, e1);
@@ -629,8 +611,8 @@ void set_tcgen05_variant(int v) { g_tcgen05_variant = v; }
 int get_tcgen05_variant() { return g_tcgen05_variant; }
 
 cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches) {
-  if (g_tcgen05_variant == 1) return launch_fwd_tcgen05_db(p, sm_count, stream, launches);
-  if (p.D == 256) return launch_fwd_tcgen05_d256(p, sm_count, stream, launches);
+  // D = 256 exists only in the double-buffered family (its accumulator leaves room for one Q tile).
+  if (g_tcgen05_variant == 1 || p.D == 256) return launch_fwd_tcgen05_db(p, sm_count, stream, launches);
   if (p.D == 128) return p.bf16 ? launch_one<128, true>(p, sm_count, stream, launches)
                                 : launch_one<128, false>(p, sm_count, stream, launches);
   if (p.D == 64) return p.bf16 ? launch_one<64, true>(p, sm_count, stream, launches)

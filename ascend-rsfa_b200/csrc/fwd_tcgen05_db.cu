@@ -11,9 +11,11 @@
 //   softmax group t           tcgen05.ld S -> mask (diagonal / ragged tiles) -> row max -> lazy
 //                             rescale -> exp2 -> row sum -> P_j (16-bit) over S_t[j & 1]
 //   O_t += P_j V_j            4 MMAs of 128 x D x 16, A = P_j from TMEM, B = V_j MN-major
+// One MMA-issuing warp per Q tile: a wait on an mbarrier costs the issuing warp about 100 cycles
+// even when it is already satisfied and a tcgen05.mma about 40, so one warp cannot feed both tiles.
 // TMEM columns: S_t[b] at 128 t + 64 b, O_t at 128 kNT + D t (kNT = 2 for D <= 128, 1 for D = 256).
 // Shared memory: Q tiles + a ring of K/V tiles of 64 keys filled by TMA (128-byte swizzle).
-// Roles: warps [0, 4 kNT) softmax (one thread per row), then one TMA warp and one MMA warp.
+// Roles: warps [0, 4 kNT) softmax (one thread per row), then one TMA warp and kNT MMA warps.
 // Work items (batch*head, block of 128 kNT rows) come from an atomic queue, head-major, causal
 // blocks heaviest first inside a head.
 #include "tcgen05_common.cuh"
@@ -31,13 +33,16 @@ struct DbCfg {
   static constexpr int kQTileBytes = kBoxes * kQBoxBytes;
   static constexpr int kKvBoxBytes = kKeysDb * 128;
   static constexpr int kKvBytes = kBoxes * kKvBoxBytes;
-  static constexpr int kStages = (D == 256) ? 4 : (D == 128 ? 8 : 12);
-  static constexpr int kThreads = 32 * (4 * NT + 2);
+  // A ring slot holds a PAIR of tiles that the MMA warps consume together: (K_0, K_1) first,
+  // then (V_j, K_{j+2}) for j = 0, 1, ... - one full/empty barrier pair per slot.
+  static constexpr int kSlotBytes = 2 * kKvBytes;
+  static constexpr int kStages = (D == 256) ? 2 : (D == 128 ? 4 : 6);
+  static constexpr int kThreads = 32 * (4 * NT + 1 + NT);
   static constexpr int kTmaWarp = 4 * NT;
-  static constexpr int kMmaWarp = 4 * NT + 1;
+  static constexpr int kMmaWarp0 = 4 * NT + 1;   // one MMA warp per Q tile
   // q_full, q_empty, pv_done, o_full per tile; s_full, p_full per (tile, buffer); ring; scheduler
   static constexpr int kNumBarriers = 4 * NT + 4 * NT + 2 * kStages + 4;
-  static constexpr int kSmemBytes = NT * kQTileBytes + kStages * kKvBytes + 1024 + kNumBarriers * 8 + 64;
+  static constexpr int kSmemBytes = NT * kQTileBytes + kStages * kSlotBytes + 1024 + kNumBarriers * 8 + 128;
   __host__ __device__ static constexpr int col_s(int t, int b) { return 128 * t + 64 * b; }
   __host__ __device__ static constexpr int col_o(int t) { return 128 * NT + D * t; }
 };
@@ -56,7 +61,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = smem_base;
   const uint32_t sKV = sQ + NT * C::kQTileBytes;
-  const uint32_t sBar = sKV + C::kStages * C::kKvBytes;
+  const uint32_t sBar = sKV + C::kStages * C::kSlotBytes;
   auto bar_q_full = [&](int t) { return sBar + 8u * t; };
   auto bar_q_empty = [&](int t) { return sBar + 8u * (NT + t); };
   auto bar_pv_done = [&](int t) { return sBar + 8u * (2 * NT + t); };   // one completion per key tile
@@ -91,16 +96,16 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     }
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_kv_full(s), 1);
-      mbar_init(bar_kv_empty(s), 1);
+      mbar_init(bar_kv_empty(s), NT);   // one commit per MMA warp
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_sched_full0 + 8u * s, 1);
-      mbar_init(bar_sched_empty0 + 8u * s, 1 + 4 * NT);  // MMA warp + one lane per softmax warp
+      mbar_init(bar_sched_empty0 + 8u * s, NT + 4 * NT);  // one lane per MMA warp and per softmax warp
     }
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == C::kMmaWarp) {
+  if (warp == C::kMmaWarp0) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), 512);
     tmem_relinquish();
   }
@@ -125,7 +130,6 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
 
   if (warp == C::kTmaWarp) {
     // ================================================================ producer
-    // Ring order = consumption order of the MMA warp: K_0, K_1, then V_j, K_{j+2} for j = 0, 1, ...
     if (lane == 0) {
       RSFA_TRACE_DECL(3);
       uint32_t kv_count = 0, item_count = 0;
@@ -144,21 +148,26 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         const int b = bh / p.H, h = bh - b * p.H;
         int nmax = 0;
         for (int t = 0; t < NT; ++t) nmax = max(nmax, num_kv_tiles_db(row0 + t * kRowsDb, S, p.causal));
-        auto load_kv = [&](const CUtensorMap* map, int j) -> bool {
+        // one ring entry: tile A (K_0 or V_j) and, when it exists, tile B (K_1 or K_{j+2})
+        auto load_pair = [&](const CUtensorMap* map_a, int ja, bool has_b, int jb) -> bool {
           const uint32_t s = kv_count % C::kStages;
           const uint32_t ph = (kv_count / C::kStages) & 1;
           if (!mbar_wait(bar_kv_empty(s), ph ^ 1, abort_flag, wait_ns, kTagKvEmpty)) return false;
-          RSFA_TRACE_EV(0x200 + j);
-          mbar_arrive_expect_tx(bar_kv_full(s), C::kKvBytes);
+          RSFA_TRACE_EV(0x200 + ja);
+          mbar_arrive_expect_tx(bar_kv_full(s), has_b ? C::kSlotBytes : C::kKvBytes);
           for (int bx = 0; bx < C::kBoxes; ++bx)
-            tma_load_4d(sKV + s * C::kKvBytes + bx * C::kKvBoxBytes, map, bar_kv_full(s), bx * 64, j * kKeysDb, h, b);
+            tma_load_4d(sKV + s * C::kSlotBytes + bx * C::kKvBoxBytes, map_a, bar_kv_full(s), bx * 64, ja * kKeysDb, h, b);
+          if (has_b) {
+            for (int bx = 0; bx < C::kBoxes; ++bx)
+              tma_load_4d(sKV + s * C::kSlotBytes + C::kKvBytes + bx * C::kKvBoxBytes, &maps.k, bar_kv_full(s), bx * 64,
+                          jb * kKeysDb, h, b);
+          }
           ++kv_count;
           return true;
         };
-        // K_0 and K_1 before the Q tiles: their slots free up while the previous item drains,
+        // (K_0, K_1) before the Q tiles: ring slots free up while the previous item drains,
         // whereas a Q buffer is released only when that item's last QK^T on it has finished.
-        ok = load_kv(&maps.k, 0);
-        if (ok && nmax > 1) ok = load_kv(&maps.k, 1);
+        ok = load_pair(&maps.k, 0, nmax > 1, 1);
         for (int t = 0; ok && t < NT; ++t) {
           ok = mbar_wait(bar_q_empty(t), (item_count & 1) ^ 1, abort_flag, wait_ns, kTagQEmpty);
           if (!ok) break;
@@ -168,17 +177,16 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
             tma_load_4d(sQ + t * C::kQTileBytes + bx * C::kQBoxBytes, &maps.q, bar_q_full(t), bx * 64,
                         row0 + t * kRowsDb, h, b);
         }
-        for (int j = 0; ok && j < nmax; ++j) {
-          ok = load_kv(&maps.v, j);
-          if (ok && j + 2 < nmax) ok = load_kv(&maps.k, j + 2);
-        }
+        for (int j = 0; ok && j < nmax; ++j) ok = load_pair(&maps.v, j, j + 2 < nmax, j + 2);
         ++item_count;
       }
     }
-  } else if (warp == C::kMmaWarp) {
-    // ============================================================== MMA issuer
+  } else if (warp >= C::kMmaWarp0) {
+    // ============================================================== MMA issuers, one warp per Q tile
     // Every lane runs this role with identical control flow (operands stay in uniform registers);
-    // only the tcgen05 instructions are issued by one elected lane.
+    // only the tcgen05 instructions are issued by one elected lane.  Both warps walk the same
+    // sequence of ring entries; a slot is free again when both have committed it.
+    const int t = warp - C::kMmaWarp0;
     const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
     auto wait_all = [&](uint32_t bar, uint32_t parity, int tag) -> bool {
       const bool r = mbar_wait(bar, parity, abort_flag, wait_ns, tag);
@@ -187,12 +195,15 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     constexpr uint32_t idesc_qk = make_idesc_f16(kRowsDb, kKeysDb, kBf16, false, false);
     constexpr uint32_t idesc_pv = make_idesc_f16(kRowsDb, D, kBf16, false, true);
     RSFA_TRACE_DECL(2);
-    const uint64_t desc_q0 = make_smem_desc_sw128(sQ, 16, 1024);
+#ifdef RSFA_TRACE
+    if (t != 0) trace_buf = nullptr;
+#endif
+    const uint64_t desc_q = make_smem_desc_sw128(sQ + t * C::kQTileBytes, 16, 1024);
     const uint64_t desc_k0 = make_smem_desc_sw128(sKV, 16, 1024);
     const uint64_t desc_v0 = make_smem_desc_sw128(sKV, C::kKvBoxBytes, 1024);
+    const uint32_t col_o = tmem_u + C::col_o(t);
     uint32_t kv_count = 0, item_count = 0;
-    uint32_t p_count[NT][2];
-    for (int t = 0; t < NT; ++t) p_count[t][0] = p_count[t][1] = 0;
+    uint32_t p_count[2] = {0, 0};
     bool ok = true;
     while (ok) {
       const int slot = item_count & 1;
@@ -204,107 +215,77 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       if (item >= sched.total_items) break;
       int bh, row0;
       decode(item, bh, row0);
-      int n[NT];
       int nmax = 0;
-      for (int t = 0; t < NT; ++t) {
-        n[t] = num_kv_tiles_db(row0 + t * kRowsDb, S, p.causal);
-        nmax = max(nmax, n[t]);
-      }
+      for (int tt = 0; tt < NT; ++tt) nmax = max(nmax, num_kv_tiles_db(row0 + tt * kRowsDb, S, p.causal));
+      const int n = num_kv_tiles_db(row0 + t * kRowsDb, S, p.causal);
       // S_t[buf] = Q_t K^T: K-major operands; 16 elements of D per step = 32 B inside a swizzle
-      // row, four steps per 64-column box.
-      auto issue_qk = [&](int t, int buf, uint32_t kslot) {
-        const uint64_t qd = desc_q0 + static_cast<uint64_t>((t * C::kQTileBytes) >> 4);
-        const uint64_t kd = desc_k0 + static_cast<uint64_t>((kslot * C::kKvBytes) >> 4);
+      // row, four steps per 64-column box.  `koff` = byte offset of the K tile in the ring.
+      auto issue_qk = [&](int buf, uint32_t koff) {
+        const uint64_t kd = desc_k0 + static_cast<uint64_t>(koff >> 4);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off_q = ((ks >> 2) * C::kQBoxBytes + (ks & 3) * 32) >> 4;
           const uint32_t off_k = ((ks >> 2) * C::kKvBoxBytes + (ks & 3) * 32) >> 4;
-          umma_ss_elect(tmem_u + C::col_s(t, buf), qd + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
+          umma_ss_elect(tmem_u + C::col_s(t, buf), desc_q + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
         }
       };
       // O_t (+)= P V: A = P in TMEM (8 columns per 16 keys), B = V MN-major, N = D spans D/64
       // boxes (kKvBoxBytes apart), 16 keys = two 8-row atoms of 1024 B.
-      auto issue_pv = [&](int t, int buf, uint32_t vslot, bool accumulate) {
-        const uint64_t vd = desc_v0 + static_cast<uint64_t>((vslot * C::kKvBytes) >> 4);
+      auto issue_pv = [&](int buf, uint32_t voff, bool accumulate) {
+        const uint64_t vd = desc_v0 + static_cast<uint64_t>(voff >> 4);
 #pragma unroll
         for (int ks = 0; ks < kKeysDb / 16; ++ks) {
-          umma_ts_elect(tmem_u + C::col_o(t), tmem_u + C::col_s(t, buf) + ks * 8, vd + ((ks * 2048) >> 4), idesc_pv,
+          umma_ts_elect(col_o, tmem_u + C::col_s(t, buf) + ks * 8, vd + ((ks * 2048) >> 4), idesc_pv,
                         (accumulate || ks > 0) ? 1u : 0u);
         }
       };
-      auto wait_kv = [&](uint32_t idx) -> bool {
-        return wait_all(bar_kv_full(idx % C::kStages), (idx / C::kStages) & 1, kTagKvFull);
-      };
 
-      for (int t = 0; ok && t < NT; ++t) ok = wait_all(bar_q_full(t), item_count & 1, kTagQFull);
+      ok = wait_all(bar_q_full(t), item_count & 1, kTagQFull);
       if (!ok) break;
-      uint32_t idx = kv_count;   // next ring entry to consume
-      // prologue: S_t[0] = Q_t K_0^T, S_t[1] = Q_t K_1^T
-      for (int j = 0; ok && j < 2 && j < nmax; ++j) {
-        ok = wait_kv(idx);
+      // entry 0: (K_0, K_1) -> S_t[0], S_t[1]
+      {
+        const uint32_t s = kv_count % C::kStages;
+        ok = wait_all(bar_kv_full(s), (kv_count / C::kStages) & 1, kTagKvFull);
         if (!ok) break;
         tc_fence_after_sync();
-        for (int t = 0; t < NT; ++t) {
-          if (j < n[t]) {
-            issue_qk(t, j, idx % C::kStages);
+        for (int j = 0; j < 2; ++j) {
+          if (j < n) {
+            issue_qk(j, s * C::kSlotBytes + j * C::kKvBytes);
             umma_commit_elect(bar_s_full(t, j));
           }
         }
-        umma_commit_elect(bar_kv_empty(idx % C::kStages));
-        ++idx;
+        if (n <= 2) umma_commit_elect(bar_q_empty(t));   // Q_t is dead after its last QK^T
+        umma_commit_elect(bar_kv_empty(s));
+        ++kv_count;
       }
-      if (!ok) break;
-      // a Q tile is dead once its last QK^T has been issued: release it for the next item
-      for (int t = 0; t < NT; ++t)
-        if (n[t] <= 2) umma_commit_elect(bar_q_empty(t));
+      // entry j + 1: (V_j, K_{j+2})
       for (int j = 0; ok && j < nmax; ++j) {
         const int buf = j & 1;
-        const uint32_t vidx = idx;
-        const uint32_t kidx = idx + 1;
-        const bool more_k = (j + 2 < nmax);
-        ok = wait_kv(vidx);   // V_j
+        const uint32_t s = kv_count % C::kStages;
+        ok = wait_all(bar_kv_full(s), (kv_count / C::kStages) & 1, kTagKvFull);
         if (!ok) break;
-        RSFA_TRACE_EV(0x6000 + j);   // V present
-        bool k_ready = false;
-        for (int t = 0; ok && t < NT; ++t) {
-          if (j < n[t]) {
-            ok = wait_all(bar_p_full(t, buf), p_count[t][buf] & 1, kTagPFull);
-            if (!ok) break;
-            ++p_count[t][buf];
-            tc_fence_after_sync();
-            RSFA_TRACE_EV(0x1000 + (t << 8) + j);   // P seen
-            issue_pv(t, buf, vidx % C::kStages, j > 0);
-            umma_commit_elect(bar_pv_done(t));
-            if (j == n[t] - 1) umma_commit_elect(bar_o_full(t));
-            RSFA_TRACE_EV(0x2000 + (t << 8) + j);   // PV issued
-          }
-          if (j + 2 < n[t]) {
-            if (!k_ready) {
-              ok = wait_kv(kidx);   // K_{j+2}
-              if (!ok) break;
-              tc_fence_after_sync();
-              k_ready = true;
-            }
-            issue_qk(t, buf, kidx % C::kStages);   // S_t[buf] is free: PV above consumed P_j in order
-            umma_commit_elect(bar_s_full(t, buf));
-            if (j + 3 == n[t]) umma_commit_elect(bar_q_empty(t));
-            RSFA_TRACE_EV(0x5000 + (t << 8) + j);   // QK(j+2) issued
-          }
+        RSFA_TRACE_EV(0x6000 + j);   // entry present
+        if (j < n) {
+          ok = wait_all(bar_p_full(t, buf), p_count[buf] & 1, kTagPFull);
+          if (!ok) break;
+          ++p_count[buf];
+          tc_fence_after_sync();
+          RSFA_TRACE_EV(0x1000 + j);   // P seen
+          issue_pv(buf, s * C::kSlotBytes, j > 0);
+          umma_commit_elect(bar_pv_done(t));
+          if (j == n - 1) umma_commit_elect(bar_o_full(t));
+          RSFA_TRACE_EV(0x2000 + j);   // PV issued
         }
-        if (!ok) break;
-        umma_commit_elect(bar_kv_empty(vidx % C::kStages));
-        ++idx;
-        if (more_k) {
-          if (!k_ready) {
-            ok = wait_kv(kidx);
-            if (!ok) break;
-          }
-          umma_commit_elect(bar_kv_empty(kidx % C::kStages));
-          ++idx;
+        if (j + 2 < n) {
+          issue_qk(buf, s * C::kSlotBytes + C::kKvBytes);   // S_t[buf] is free: PV above consumed P_j in order
+          umma_commit_elect(bar_s_full(t, buf));
+          if (j + 3 == n) umma_commit_elect(bar_q_empty(t));
+          RSFA_TRACE_EV(0x5000 + j);   // QK(j+2) issued
         }
+        umma_commit_elect(bar_kv_empty(s));
+        ++kv_count;
       }
       if (!ok) break;
-      kv_count = idx;
       ++item_count;
     }
   } else {
@@ -500,7 +481,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  if (warp == C::kMmaWarp) tmem_dealloc(tmem_base, 512);
+  if (warp == C::kMmaWarp0) tmem_dealloc(tmem_base, 512);
   if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
 }
 

@@ -92,34 +92,6 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
 }
 
 
-// exp2 of two lanes on the FMA pipe instead of the MUFU: round-to-nearest split x = n + r with
-// |r| <= 0.5 (adding 1.5 * 2^23 leaves n in the low mantissa bits), a cubic for 2^r (maximum
-// relative error 7.6e-5, below half an ulp of the 16-bit P it is rounded to), and n added into
-// the exponent field.  The MUFU does 16 ex2 per clock per SM, which at D <= 128 takes as long as
-// the tile's MMAs; moving a fraction of the exponentials here shortens the softmax critical path.
-// Inputs are clamped at -126 so the exponent arithmetic cannot wrap (masked scores are -inf).
-__device__ __forceinline__ void exp2_poly_x2(uint64_t x2v, float& e0, float& e1) {
-  float x0, x1;
-  unpack_f32x2(x2v, x0, x1);
-  x0 = fmaxf(x0, -126.f);
-  x1 = fmaxf(x1, -126.f);
-  const uint64_t xc = pack_f32x2(x0, x1);
-  const uint64_t magic = pack_f32x2(12582912.f, 12582912.f);
-  const uint64_t neg_magic = pack_f32x2(-12582912.f, -12582912.f);
-  const uint64_t minus1 = pack_f32x2(-1.f, -1.f);
-  const uint64_t t = add_f32x2(xc, magic);
-  const uint64_t n = add_f32x2(t, neg_magic);
-  const uint64_t r = fma_f32x2(n, minus1, xc);
-  uint64_t q = fma_f32x2(pack_f32x2(0.055205513f, 0.055205513f), r, pack_f32x2(0.24261397f, 0.24261397f));
-  q = fma_f32x2(q, r, pack_f32x2(0.69325477f, 0.69325477f));
-  q = fma_f32x2(q, r, pack_f32x2(0.9999277f, 0.9999277f));
-  float t0, t1, q0, q1;
-  unpack_f32x2(t, t0, t1);
-  unpack_f32x2(q, q0, q1);
-  e0 = __uint_as_float((__float_as_uint(t0) << 23) + __float_as_uint(q0));
-  e1 = __uint_as_float((__float_as_uint(t1) << 23) + __float_as_uint(q1));
-}
-
 // Register budgets per warpgroup after the common set-up (launch allocates 168 each):
 // 2 x 128 x 208 + 128 x 80 = 63488 of 65536, so the increase never waits on an exact fit.
 constexpr int kRegsSoftmax = 208;

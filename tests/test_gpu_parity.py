@@ -115,6 +115,20 @@ def test_both_kernel_families_agree(fa, cuda_device, path, causal):
         fa.set_option("force_path", -1)
 
 
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("causal", [False, True])
+def test_both_tcgen05_variants(fa, cuda_device, variant, causal):
+    """Single-buffered (128-key tiles) and double-buffered (64-key tiles) kernels of the tcgen05 family."""
+    fa.set_option("tcgen05_variant", variant)
+    try:
+        for B, H, S, D, scale in [(2, 2, 1024, 128, 0.5), (1, 3, 1536, 64, 0.125), (1, 2, 449, 128, 0.3),
+                                  (1, 2, 191, 64, 0.3), (1, 1, 2048, 128, 2.0)]:
+            q, k, v = make_inputs(B, H, S, D, seed=S + D)
+            check(fa, q, k, v, causal, scale, 128, 128, cuda_device)
+    finally:
+        fa.set_option("tcgen05_variant", 0)
+
+
 def test_result_does_not_depend_on_requested_tile(fa, cuda_device):
     q, k, v = make_inputs(1, 2, 512, 64, seed=4)
     outs = [fa.attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), True, 0.5, bm, bn)
