@@ -64,8 +64,9 @@ struct Cfg {
   static constexpr int kStages = (D == 128) ? 4 : 6;
   static constexpr int kQBoxBytes = kTileM * 128;             // 128 rows x 128 B
   static constexpr int kKvBoxBytes = kTileN * 128;
-  static constexpr int kNumBarriers = 2 * kNT + 2 * kStages + 4 * kNT + 4;
-  static constexpr int kSmemBytes = kNT * kQTileBytes + kStages * kKvTileBytes + 1024 /*align*/ +
+  static constexpr int kStageBytes = kTileM * 128;            // epilogue staging: 128 rows x 64 columns
+  static constexpr int kNumBarriers = 2 * kNT + 2 * kStages + 5 * kNT + 4;
+  static constexpr int kSmemBytes = kNT * kQTileBytes + kStages * kKvTileBytes + kNT * kStageBytes + 1024 /*align*/ +
                                     kNumBarriers * 8 + 64;
   __host__ __device__ static constexpr int kColS(int t) { return t * kTileN; }
   __host__ __device__ static constexpr int kColO(int t) { return 2 * kTileN + t * D; }
@@ -87,7 +88,8 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = smem_base;
   const uint32_t sKV = sQ + kNT * C::kQTileBytes;
-  const uint32_t sBar = sKV + C::kStages * C::kKvTileBytes;
+  const uint32_t sStage = sKV + C::kStages * C::kKvTileBytes;   // one staging buffer per softmax group
+  const uint32_t sBar = sStage + kNT * C::kStageBytes;
   // barrier addresses
   auto bar_q_full = [&](int t) { return sBar + 8u * t; };
   auto bar_q_empty = [&](int t) { return sBar + 8u * (kNT + t); };
@@ -97,7 +99,8 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   // P_t is handed to the MMA warp in two halves of 64 keys so the first PV MMAs start early.
   auto bar_p_full = [&](int t, int half) { return sBar + 8u * (3 * kNT + 2 * C::kStages + 2 * t + half); };
   auto bar_o_full = [&](int t) { return sBar + 8u * (5 * kNT + 2 * C::kStages + t); };
-  const uint32_t bar_sched_full0 = sBar + 8u * (6 * kNT + 2 * C::kStages);  // 2 slots
+  auto bar_epi = [&](int t) { return sBar + 8u * (6 * kNT + 2 * C::kStages + t); };   // group-wide sync of the epilogue
+  const uint32_t bar_sched_full0 = sBar + 8u * (7 * kNT + 2 * C::kStages);  // 2 slots
   const uint32_t bar_sched_empty0 = bar_sched_full0 + 16u;                   // 2 slots
   const uint32_t misc = sBar + 8u * C::kNumBarriers;
   // misc words: [0] TMEM base, [1] abort flag, [2..3] scheduler ring
@@ -119,6 +122,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       mbar_init(bar_p_full(t, 0), kTileM);
       mbar_init(bar_p_full(t, 1), kTileM);
       mbar_init(bar_o_full(t), 1);
+      mbar_init(bar_epi(t), kTileM);
     }
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_kv_full(s), 1);
@@ -139,6 +143,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
     tma_prefetch_desc(&maps.q);
     tma_prefetch_desc(&maps.k);
     tma_prefetch_desc(&maps.v);
+    tma_prefetch_desc(&maps.o);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -361,7 +366,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
     const uint32_t tS = tmem_base + lane_base + C::kColS(t);
     const uint32_t tO = tmem_base + lane_base + C::kColO(t);
     const float scale_log2 = p.sm_scale * kLog2e;
-    uint32_t item_count = 0, s_count = 0, o_count = 0;
+    uint32_t item_count = 0, s_count = 0, o_count = 0, epi_count = 0;
     bool ok = true;
 #ifdef RSFA_TRACE
     unsigned long long* trace_buf = (p.trace != nullptr && blockIdx.x == 0 && (warp & 3) == 0 && lane == 0)
@@ -537,31 +542,58 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       RSFA_TRACE_EV(0x6000);         // O complete seen
       const float inv_l = 1.f / l;
       const int b = bh / p.H, h = bh - b * p.H;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_stride[0] + h * p.o_stride[1] +
-                       static_cast<int64_t>(row) * p.o_stride[2];
+      // O_t / l goes to global memory through a 128-byte-swizzled staging buffer and one TMA store
+      // per 64 columns: a thread owns a whole row, so direct stores would touch 32 different
+      // lines per instruction.  Rows past S are clipped by the TMA store.
+      const uint32_t stage = sStage + t * C::kStageBytes;
+      const bool issuer = (row_in_tile == 0);
+      auto group_sync = [&]() -> bool {
+        mbar_arrive(bar_epi(t));
+        bool r = mbar_wait(bar_epi(t), epi_count & 1, abort_flag, wait_ns, kTagEpilogue);
+        ++epi_count;
+        return __all_sync(0xffffffffu, r) != 0;
+      };
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t o[32];
-        tmem_ld_x32(tO + c0, o);
+      for (int c0 = 0; c0 < D; c0 += 64) {
+        uint32_t o0[32], o1[32];
+        tmem_ld_x32(tO + c0, o0);
+        tmem_ld_x32(tO + c0 + 32, o1);
         tmem_wait_ld();
-        reg_fence_x32(o);
-        if (row < S) {
+        reg_fence_x32(o0);
+        reg_fence_x32(o1);
+        if (issuer) tma_store_wait_read();   // the previous store no longer reads the staging buffer
+        ok = group_sync();
+        if (!ok) break;
+        const uint32_t row_addr = stage + row_in_tile * 128;
+        const uint32_t sw = static_cast<uint32_t>(row_in_tile & 7);
 #pragma unroll
-          for (int c = 0; c < 32; c += 8) {
-            uint4 v4;
-            v4.x = pack2<kBf16>(__uint_as_float(o[c + 0]) * inv_l, __uint_as_float(o[c + 1]) * inv_l);
-            v4.y = pack2<kBf16>(__uint_as_float(o[c + 2]) * inv_l, __uint_as_float(o[c + 3]) * inv_l);
-            v4.z = pack2<kBf16>(__uint_as_float(o[c + 4]) * inv_l, __uint_as_float(o[c + 5]) * inv_l);
-            v4.w = pack2<kBf16>(__uint_as_float(o[c + 6]) * inv_l, __uint_as_float(o[c + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c0 + c) = v4;
-          }
+        for (int c = 0; c < 32; c += 8) {
+          st_shared_v4(row_addr + (((c >> 3) ^ sw) << 4),
+                       pack2<kBf16>(__uint_as_float(o0[c + 0]) * inv_l, __uint_as_float(o0[c + 1]) * inv_l),
+                       pack2<kBf16>(__uint_as_float(o0[c + 2]) * inv_l, __uint_as_float(o0[c + 3]) * inv_l),
+                       pack2<kBf16>(__uint_as_float(o0[c + 4]) * inv_l, __uint_as_float(o0[c + 5]) * inv_l),
+                       pack2<kBf16>(__uint_as_float(o0[c + 6]) * inv_l, __uint_as_float(o0[c + 7]) * inv_l));
+          st_shared_v4(row_addr + ((((c >> 3) + 4) ^ sw) << 4),
+                       pack2<kBf16>(__uint_as_float(o1[c + 0]) * inv_l, __uint_as_float(o1[c + 1]) * inv_l),
+                       pack2<kBf16>(__uint_as_float(o1[c + 2]) * inv_l, __uint_as_float(o1[c + 3]) * inv_l),
+                       pack2<kBf16>(__uint_as_float(o1[c + 4]) * inv_l, __uint_as_float(o1[c + 5]) * inv_l),
+                       pack2<kBf16>(__uint_as_float(o1[c + 6]) * inv_l, __uint_as_float(o1[c + 7]) * inv_l));
+        }
+        fence_proxy_async();
+        ok = group_sync();
+        if (!ok) break;
+        if (issuer) {
+          tma_store_4d(&maps.o, stage, c0, tile_row0, h, b);
+          tma_store_commit();
         }
       }
+      if (!ok) break;
       if (p.lse != nullptr && row < S)
         p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);
       tc_fence_before_sync();
       RSFA_TRACE_EV(0x7000);         // epilogue done
     }
+    if (row_in_tile == 0) tma_store_wait_all();   // the last TMA stores must be complete before the CTA exits
   }
 
   // ------------------------------------------------------------------ teardown
@@ -583,7 +615,7 @@ cudaError_t launch_one(const FwdParams& p, int sm_count, cudaStream_t stream, lo
   using C = Cfg<D>;
   TmaMaps maps;
   if (!make_map(&maps.q, p.q, p, p.q_stride, kTileM) || !make_map(&maps.k, p.k, p, p.k_stride, kTileN) ||
-      !make_map(&maps.v, p.v, p, p.v_stride, kTileN))
+      !make_map(&maps.v, p.v, p, p.v_stride, kTileN) || !make_map(&maps.o, p.o, p, p.o_stride, kTileM))
     return cudaErrorInvalidValue;
   SchedInfo sched;
   sched.items_per_head = (p.S + kNT * kTileM - 1) / (kNT * kTileM);

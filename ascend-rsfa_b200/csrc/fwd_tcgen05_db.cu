@@ -41,8 +41,9 @@ struct DbCfg {
   static constexpr int kTmaWarp = 4 * NT;
   static constexpr int kMmaWarp0 = 4 * NT + 1;   // one MMA warp per Q tile
   // q_full, q_empty, pv_done, o_full per tile; s_full, p_full per (tile, buffer); ring; scheduler
-  static constexpr int kNumBarriers = 4 * NT + 4 * NT + 2 * kStages + 4;
-  static constexpr int kSmemBytes = NT * kQTileBytes + kStages * kSlotBytes + 1024 + kNumBarriers * 8 + 128;
+  static constexpr int kStageBytes = kRowsDb * 128;   // epilogue staging: 128 rows x 64 columns
+  static constexpr int kNumBarriers = 4 * NT + 4 * NT + NT + 2 * kStages + 4;
+  static constexpr int kSmemBytes = NT * kQTileBytes + kStages * kSlotBytes + NT * kStageBytes + 1024 + kNumBarriers * 8 + 128;
   __host__ __device__ static constexpr int col_s(int t, int b) { return 128 * t + 64 * b; }
   __host__ __device__ static constexpr int col_o(int t) { return 128 * NT + D * t; }
 };
@@ -61,7 +62,8 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = smem_base;
   const uint32_t sKV = sQ + NT * C::kQTileBytes;
-  const uint32_t sBar = sKV + C::kStages * C::kSlotBytes;
+  const uint32_t sStage = sKV + C::kStages * C::kSlotBytes;   // one staging buffer per softmax group
+  const uint32_t sBar = sStage + NT * C::kStageBytes;
   auto bar_q_full = [&](int t) { return sBar + 8u * t; };
   auto bar_q_empty = [&](int t) { return sBar + 8u * (NT + t); };
   auto bar_pv_done = [&](int t) { return sBar + 8u * (2 * NT + t); };   // one completion per key tile
@@ -70,7 +72,8 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   auto bar_p_full = [&](int t, int b) { return sBar + 8u * (6 * NT + 2 * t + b); };
   auto bar_kv_full = [&](int s) { return sBar + 8u * (8 * NT + s); };
   auto bar_kv_empty = [&](int s) { return sBar + 8u * (8 * NT + C::kStages + s); };
-  const uint32_t bar_sched_full0 = sBar + 8u * (8 * NT + 2 * C::kStages);  // 2 slots
+  auto bar_epi = [&](int t) { return sBar + 8u * (8 * NT + 2 * C::kStages + t); };   // group-wide sync of the epilogue
+  const uint32_t bar_sched_full0 = sBar + 8u * (9 * NT + 2 * C::kStages);  // 2 slots
   const uint32_t bar_sched_empty0 = bar_sched_full0 + 16u;                 // 2 slots
   const uint32_t misc = sBar + 8u * C::kNumBarriers;
   uint8_t* misc_ptr = smem_raw + (misc - smem_u32(smem_raw));
@@ -89,6 +92,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       mbar_init(bar_q_empty(t), 1);
       mbar_init(bar_pv_done(t), 1);
       mbar_init(bar_o_full(t), 1);
+      mbar_init(bar_epi(t), kRowsDb);
       for (int b = 0; b < 2; ++b) {
         mbar_init(bar_s_full(t, b), 1);
         mbar_init(bar_p_full(t, b), kRowsDb);
@@ -113,6 +117,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     tma_prefetch_desc(&maps.q);
     tma_prefetch_desc(&maps.k);
     tma_prefetch_desc(&maps.v);
+    tma_prefetch_desc(&maps.o);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -295,7 +300,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tO = tmem_base + lane_base + C::col_o(t);
     const float scale_log2 = p.sm_scale * kLog2e;
-    uint32_t item_count = 0, o_count = 0, pv_count = 0;
+    uint32_t item_count = 0, o_count = 0, pv_count = 0, epi_count = 0;
     uint32_t s_count[2] = {0, 0};
     bool ok = true;
 #ifdef RSFA_TRACE
@@ -444,31 +449,58 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       RSFA_TRACE_EV(0x6000);   // O seen
       const float inv_l = 1.f / l;
       const int b = bh / p.H, h = bh - b * p.H;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_stride[0] + h * p.o_stride[1] +
-                       static_cast<int64_t>(row) * p.o_stride[2];
+      // O_t / l goes to global memory through a 128-byte-swizzled staging buffer and one TMA store
+      // per 64 columns: a thread owns a whole row, so direct stores would touch 32 different
+      // lines per instruction.  Rows past S are clipped by the TMA store.
+      const uint32_t stage = sStage + t * C::kStageBytes;
+      const bool issuer = (row_in_tile == 0);
+      auto group_sync = [&]() -> bool {
+        mbar_arrive(bar_epi(t));
+        bool r = mbar_wait(bar_epi(t), epi_count & 1, abort_flag, wait_ns, kTagEpilogue);
+        ++epi_count;
+        return __all_sync(0xffffffffu, r) != 0;
+      };
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t o[32];
-        tmem_ld_x32(tO + c0, o);
+      for (int c0 = 0; c0 < D; c0 += 64) {
+        uint32_t o0[32], o1[32];
+        tmem_ld_x32(tO + c0, o0);
+        tmem_ld_x32(tO + c0 + 32, o1);
         tmem_wait_ld();
-        reg_fence_x32(o);
-        if (row < S) {
+        reg_fence_x32(o0);
+        reg_fence_x32(o1);
+        if (issuer) tma_store_wait_read();   // the previous store no longer reads the staging buffer
+        ok = group_sync();
+        if (!ok) break;
+        const uint32_t row_addr = stage + row_in_tile * 128;
+        const uint32_t sw = static_cast<uint32_t>(row_in_tile & 7);
 #pragma unroll
-          for (int c = 0; c < 32; c += 8) {
-            uint4 v4;
-            v4.x = pack2<kBf16>(__uint_as_float(o[c + 0]) * inv_l, __uint_as_float(o[c + 1]) * inv_l);
-            v4.y = pack2<kBf16>(__uint_as_float(o[c + 2]) * inv_l, __uint_as_float(o[c + 3]) * inv_l);
-            v4.z = pack2<kBf16>(__uint_as_float(o[c + 4]) * inv_l, __uint_as_float(o[c + 5]) * inv_l);
-            v4.w = pack2<kBf16>(__uint_as_float(o[c + 6]) * inv_l, __uint_as_float(o[c + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c0 + c) = v4;
-          }
+        for (int c = 0; c < 32; c += 8) {
+          st_shared_v4(row_addr + (((c >> 3) ^ sw) << 4),
+                       pack2<kBf16>(__uint_as_float(o0[c + 0]) * inv_l, __uint_as_float(o0[c + 1]) * inv_l),
+                       pack2<kBf16>(__uint_as_float(o0[c + 2]) * inv_l, __uint_as_float(o0[c + 3]) * inv_l),
+                       pack2<kBf16>(__uint_as_float(o0[c + 4]) * inv_l, __uint_as_float(o0[c + 5]) * inv_l),
+                       pack2<kBf16>(__uint_as_float(o0[c + 6]) * inv_l, __uint_as_float(o0[c + 7]) * inv_l));
+          st_shared_v4(row_addr + ((((c >> 3) + 4) ^ sw) << 4),
+                       pack2<kBf16>(__uint_as_float(o1[c + 0]) * inv_l, __uint_as_float(o1[c + 1]) * inv_l),
+                       pack2<kBf16>(__uint_as_float(o1[c + 2]) * inv_l, __uint_as_float(o1[c + 3]) * inv_l),
+                       pack2<kBf16>(__uint_as_float(o1[c + 4]) * inv_l, __uint_as_float(o1[c + 5]) * inv_l),
+                       pack2<kBf16>(__uint_as_float(o1[c + 6]) * inv_l, __uint_as_float(o1[c + 7]) * inv_l));
+        }
+        fence_proxy_async();
+        ok = group_sync();
+        if (!ok) break;
+        if (issuer) {
+          tma_store_4d(&maps.o, stage, c0, tile_row0, h, b);
+          tma_store_commit();
         }
       }
+      if (!ok) break;
       if (p.lse != nullptr && row < S)
         p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);
       tc_fence_before_sync();
       RSFA_TRACE_EV(0x7000);   // epilogue done
     }
+    if (row_in_tile == 0) tma_store_wait_all();   // the last TMA stores must be complete before the CTA exits
   }
 
   // ------------------------------------------------------------------ teardown
@@ -490,7 +522,7 @@ cudaError_t launch_db(const FwdParams& p, int sm_count, cudaStream_t stream, lon
   using C = DbCfg<D, NT>;
   TmaMaps maps;
   if (!make_map(&maps.q, p.q, p, p.q_stride, kRowsDb) || !make_map(&maps.k, p.k, p, p.k_stride, kKeysDb) ||
-      !make_map(&maps.v, p.v, p, p.v_stride, kKeysDb))
+      !make_map(&maps.v, p.v, p, p.v_stride, kKeysDb) || !make_map(&maps.o, p.o, p, p.o_stride, kRowsDb))
     return cudaErrorInvalidValue;
   SchedInfo sched;
   sched.items_per_head = (p.S + NT * kRowsDb - 1) / (NT * kRowsDb);

@@ -16,7 +16,7 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 // Wait-site tags (reported in the status word when a wait runs out).
 enum : int {
-  kTagQEmpty = 1, kTagKvEmpty, kTagQFull, kTagKvFull, kTagPFull, kTagSFull, kTagOFull, kTagSched
+  kTagQEmpty = 1, kTagKvEmpty, kTagQFull, kTagKvFull, kTagPFull, kTagSFull, kTagOFull, kTagSched, kTagEpilogue
 };
 
 // Debug builds (-DRSFA_TRACE) log (clock, code) pairs per role for CTA 0; the product build
@@ -40,7 +40,7 @@ constexpr int kTraceCap = 4096;
 #endif
 
 struct TmaMaps {
-  CUtensorMap q, k, v;
+  CUtensorMap q, k, v, o;
 };
 
 struct SchedInfo {
