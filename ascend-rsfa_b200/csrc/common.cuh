@@ -20,6 +20,7 @@ struct FwdParams {
   int causal;
   float sm_scale;
   int bf16;
+  int tile_n;   // keys per tile on the tcgen05 path: 128 (single-buffered S) or 64 (double-buffered S)
   int* status;                 // device status word, never null
   unsigned int* tile_counter;  // device work-queue counter (persistent kernel)
   unsigned long long wait_limit_ns;
@@ -36,10 +37,10 @@ cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t st
 // The double-buffered-S family (D = 64, 128, 256), selected by launch_fwd_tcgen05.
 cudaError_t launch_fwd_tcgen05_db(const FwdParams& p, int sm_count, cudaStream_t stream,
                                   long long* launches);
-// Kernel variant of the tcgen05 family for D <= 128: 0 = single-buffered S (two Q tiles
-// ping-pong, 128-key tiles), 1 = double-buffered S with 64-key tiles.  D = 256 always uses the latter.
-void set_tcgen05_variant(int v);
-int get_tcgen05_variant();
+// Tile the tcgen05 family runs for a problem: the requested (block_m, block_n) when that tile is
+// instantiated for D, otherwise the tile table's row for (S, D, causal).  `variant` = -1 lets the
+// request / table decide, 0 forces 128-key tiles, 1 forces 64-key tiles (D <= 128 only).
+void tcgen05_resolve_tile(int S, int D, int causal, int req_bm, int req_bn, int variant, int* bm, int* bn);
 // Adds to the process-wide kernel-launch counter behind rsfa_launch_count().
 void count_launches(long long n);
 // True when the tcgen05 kernel is instantiated for this head dimension.

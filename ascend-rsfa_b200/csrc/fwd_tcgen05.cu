@@ -638,13 +638,42 @@ bool tcgen05_supports(int S, int D, float sm_scale) {
   return (D == 64 || D == 128 || D == 256) && S >= 1 && sm_scale > 0.f;
 }
 
-static int g_tcgen05_variant = 0;
-void set_tcgen05_variant(int v) { g_tcgen05_variant = v; }
-int get_tcgen05_variant() { return g_tcgen05_variant; }
+namespace {
+struct TileRow {
+  int s_min, s_max, d, causal, bm, bn;
+};
+const TileRow kTileTable[] = {
+#include "tile_table.inc"
+};
+}  // namespace
+
+void tcgen05_resolve_tile(int S, int D, int causal, int req_bm, int req_bn, int variant, int* bm, int* bn) {
+  *bm = 128;
+  if (D == 256) {  // one instantiation only
+    *bn = 64;
+    return;
+  }
+  if (variant == 0 || variant == 1) {
+    *bn = variant == 0 ? 128 : 64;
+    return;
+  }
+  if (req_bm == 128 && (req_bn == 128 || req_bn == 64)) {  // an instantiated tile: honour the request
+    *bn = req_bn;
+    return;
+  }
+  *bn = 128;
+  for (const TileRow& r : kTileTable) {
+    if (S >= r.s_min && S <= r.s_max && D == r.d && (causal != 0) == (r.causal != 0)) {
+      *bm = r.bm;
+      *bn = r.bn;
+      return;
+    }
+  }
+}
 
 cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches) {
   // D = 256 exists only in the double-buffered family (its accumulator leaves room for one Q tile).
-  if (g_tcgen05_variant == 1 || p.D == 256) return launch_fwd_tcgen05_db(p, sm_count, stream, launches);
+  if (p.tile_n == 64 || p.D == 256) return launch_fwd_tcgen05_db(p, sm_count, stream, launches);
   if (p.D == 128) return p.bf16 ? launch_one<128, true>(p, sm_count, stream, launches)
                                 : launch_one<128, false>(p, sm_count, stream, launches);
   if (p.D == 64) return p.bf16 ? launch_one<64, true>(p, sm_count, stream, launches)
@@ -736,7 +765,7 @@ extern "C" int rsfa_fwd_noalloc(const void* q, const void* k, const void* v, voi
   }
   // Only the tcgen05 kernel uses scratch; shapes it is not built for have no variant here.
   if (!tcgen05_supports(S, D, sm_scale)) return RSFA_ERR_UNSUPPORTED;
-  const int rows_per_item = (D == 256) ? kTileM : kNT * kTileM;
+  const int rows_per_item = (D == 256) ? kTileM : kNT * kTileM;   // both families use 256-row items at D <= 128
   const long long items = static_cast<long long>(B) * H * ((S + rows_per_item - 1) / rows_per_item);
   if (items > kNoAllocMaxItems) return RSFA_ERR_TOO_LARGE;
 
@@ -768,6 +797,11 @@ extern "C" int rsfa_fwd_noalloc(const void* q, const void* k, const void* v, voi
   p.causal = causal ? 1 : 0;
   p.sm_scale = sm_scale;
   p.bf16 = (dtype == RSFA_DTYPE_BF16) ? 1 : 0;
+  {
+    int bm = 0, bn = 0;
+    tcgen05_resolve_tile(S, D, causal, 0, 0, -1, &bm, &bn);   // no tile request here: the table decides
+    p.tile_n = bn;
+  }
   p.tile_counter = d->scratch;      // cleared by the launcher on `stream` before the kernel
   p.status = reinterpret_cast<int*>(d->scratch + 1);
   p.wait_limit_ns = 2000ull * 1000000ull;

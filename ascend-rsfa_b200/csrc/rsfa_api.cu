@@ -38,6 +38,7 @@ std::atomic<long long> g_launches{0};
 std::atomic<long long> g_force_path{-1};
 std::atomic<long long> g_wait_limit_ms{2000};
 std::atomic<long long> g_host_slab_heads{0};
+std::atomic<long long> g_tcgen05_variant{-1};
 #ifdef RSFA_TRACE
 std::atomic<long long> g_trace_ptr{0};
 #endif
@@ -86,10 +87,11 @@ int choose_path(int S, int D, float sm_scale) {
   return (tc_ok && S > 128) ? RSFA_PATH_TCGEN05 : RSFA_PATH_GENERIC;
 }
 
-void tile_of_path(int path, int D, int* bm, int* bn) {
+// Tile a call runs: on the tcgen05 path the request is honoured when instantiated, otherwise the
+// tile table decides; the generic kernel has one tile per head dimension.
+void tile_of_path(int path, int S, int D, int causal, int req_bm, int req_bn, int* bm, int* bn) {
   if (path == RSFA_PATH_TCGEN05) {
-    *bm = 128;
-    *bn = (D >= 256) ? 64 : 128;
+    rsfa::tcgen05_resolve_tile(S, D, causal, req_bm, req_bn, static_cast<int>(g_tcgen05_variant.load()), bm, bn);
   } else {
     *bm = 64;
     *bn = (D >= 256) ? 32 : 64;
@@ -140,8 +142,8 @@ int rsfa_set_option(const char* name, long long value) {
   }
 #endif
   if (std::strcmp(name, "tcgen05_variant") == 0) {
-    if (value < 0 || value > 1) return RSFA_ERR_INVALID_ARGUMENT;
-    rsfa::set_tcgen05_variant(static_cast<int>(value));
+    if (value < -1 || value > 1) return RSFA_ERR_INVALID_ARGUMENT;
+    g_tcgen05_variant.store(value);
     return RSFA_OK;
   }
   if (std::strcmp(name, "host_slab_heads") == 0) {
@@ -157,7 +159,7 @@ long long rsfa_get_option(const char* name) {
   if (std::strcmp(name, "force_path") == 0) return g_force_path.load();
   if (std::strcmp(name, "wait_limit_ms") == 0) return g_wait_limit_ms.load();
   if (std::strcmp(name, "host_slab_heads") == 0) return g_host_slab_heads.load();
-  if (std::strcmp(name, "tcgen05_variant") == 0) return rsfa::get_tcgen05_variant();
+  if (std::strcmp(name, "tcgen05_variant") == 0) return g_tcgen05_variant.load();
   return RSFA_ERR_INVALID_ARGUMENT;
 }
 
@@ -170,26 +172,24 @@ int rsfa_sm_count(int device) {
 
 int rsfa_select_path(int S, int D, int causal, float sm_scale, int block_m, int block_n, int dtype,
                      int* path, int* tile_m, int* tile_n) {
-  (void)causal;
   if (path == nullptr || S < 1 || !valid_head_dim(D) || block_m < 1 || block_n < 1 ||
       (dtype != RSFA_DTYPE_F16 && dtype != RSFA_DTYPE_BF16))
     return RSFA_ERR_INVALID_ARGUMENT;
   *path = choose_path(S, D, sm_scale);
   int bm, bn;
-  tile_of_path(*path, D, &bm, &bn);
+  tile_of_path(*path, S, D, causal, block_m, block_n, &bm, &bn);
   if (tile_m != nullptr) *tile_m = bm;
   if (tile_n != nullptr) *tile_n = bn;
   return RSFA_OK;
 }
 
 int rsfa_get_tiling(int B, int H, int S, int D, int causal, int* block_m, int* block_n) {
-  (void)causal;
   if (block_m == nullptr || block_n == nullptr || B < 1 || H < 1 || S < 1 || !valid_head_dim(D))
     return RSFA_ERR_INVALID_ARGUMENT;
   // The table: one row per (S bucket, D); the causal flag does not change the tile because the
   // diagonal is handled by a masked variant of the same tile.  sm_scale is taken as positive here.
   const int path = (rsfa::tcgen05_supports(S, D, 1.0f) && S > 128) ? RSFA_PATH_TCGEN05 : RSFA_PATH_GENERIC;
-  tile_of_path(path, D, block_m, block_n);
+  tile_of_path(path, S, D, causal, 0, 0, block_m, block_n);
   return RSFA_OK;
 }
 
@@ -272,6 +272,11 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   long long launches = 0;
   cudaError_t e;
   const int path = choose_path(S, D, sm_scale);
+  {
+    int bm = 0, bn = 0;
+    tile_of_path(path, S, D, causal, block_m, block_n, &bm, &bn);
+    p.tile_n = bn;
+  }
   if (path == RSFA_PATH_TCGEN05)
     e = rsfa::launch_fwd_tcgen05(p, d->sm_count, static_cast<cudaStream_t>(stream), &launches);
   else

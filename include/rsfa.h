@@ -142,9 +142,9 @@ RSFA_API long long rsfa_launch_count(void);
 
 /*
  * Tuning / test knobs.  Names: "force_path" (-1 auto, 0 generic, 1 tcgen05),
- * "wait_limit_ms" (bound of every in-kernel wait, default 2000), "tcgen05_variant" (kernel of the
- * tcgen05 family for D <= 128: 0 single-buffered S with 128-key tiles, 1 double-buffered S with
- * 64-key tiles), "host_slab_heads"
+ * "wait_limit_ms" (bound of every in-kernel wait, default 2000), "tcgen05_variant" (-1: the requested tile if
+ * instantiated, else the tile table; 0 / 1 force the single-buffered 128-key / double-buffered 64-key
+ * kernel for D <= 128), "host_slab_heads"
  * (heads per staging slab of rsfa_fwd_host, 0 = automatic).
  * Unknown names -> RSFA_ERR_INVALID_ARGUMENT.
  */

@@ -49,6 +49,10 @@ def test_path_selection_follows_the_short_sequence_rule():
     assert fa.select_path(2048, 32, False, 0.5)[0] == _capi.RSFA_PATH_GENERIC    # D = 32 not on tcgen05
     assert fa.select_path(2048, 128, False, -0.5)[0] == _capi.RSFA_PATH_GENERIC  # non-positive scale
     assert fa.select_path(2048, 128, False, 0.5) == (1, 128, 128)
+    # an instantiated tile is honoured, anything else is replaced by the table's row
+    assert fa.select_path(2048, 128, False, 0.5, 128, 64) == (1, 128, 64)
+    assert fa.select_path(2048, 128, False, 0.5, 32, 512) == (1,) + fa.get_tiling(1, 1, 2048, 128, False)
+    assert fa.select_path(1024, 256, True, 0.0625, 128, 128) == (1, 128, 64)   # D = 256 has one tile
 
 
 def test_rsfa_fwd_argument_errors_need_no_device():

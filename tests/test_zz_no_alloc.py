@@ -36,11 +36,16 @@ def test_noalloc_matches_regular_entry_point_twice(cuda_device, B, H, S, D, caus
     q, k, v = [torch.randn(B, H, S, D, generator=g, device=dev).half() for _ in range(3)]
     stream = torch.cuda.current_stream().cuda_stream
 
+    # The allocation-free call takes no tile request (the tile table decides), so ask the regular
+    # entry point for the table's tile: both then run the same kernel and must agree bit for bit.
+    bm, bn = ctypes.c_int(0), ctypes.c_int(0)
+    assert lib.rsfa_get_tiling(B, H, S, D, int(causal), ctypes.byref(bm), ctypes.byref(bn)) == _capi.RSFA_OK
+
     def regular():
         o = torch.empty_like(q)
         lse = torch.empty(B, H, S, dtype=torch.float32, device=dev)
         rc = lib.rsfa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, H, S, D,
-                          _strides(q, k, v, o), int(causal), scale, 128, 128, _capi.RSFA_DTYPE_F16, stream)
+                          _strides(q, k, v, o), int(causal), scale, bm.value, bn.value, _capi.RSFA_DTYPE_F16, stream)
         assert rc == _capi.RSFA_OK, _capi.strerror(rc)
         return o, lse
 
