@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout and upstream Triton:
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 The reference's kernels are TritonAscend programs; upstream Triton's CPU
 interpreter (TRITON_INTERPRET=1) executes them when three shims are in place:
@@ -60,7 +60,9 @@ CASES = [
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to the reference checkout>")
+    root = sys.argv[1]
     mod = load_reference(root)
     here = os.path.dirname(os.path.abspath(__file__))
     for name, B, H, S, D, causal, scale, bm, bn, seed, std in CASES:
