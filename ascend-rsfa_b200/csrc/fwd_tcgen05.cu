@@ -24,7 +24,7 @@
 //   S_t = Q_t K_j^T          tcgen05.mma, both operands from shared memory
 //   softmax group t          tcgen05.ld S_t -> running max, exp2, row sum -> P_t
 //                            (16-bit) written back over S_t with tcgen05.st; when a
-//                            row's max grew by more than 2^8 the group rescales its
+//                            row's max grew by more than 2^13 the group rescales its
 //                            O_t rows in TMEM first (the reference's "rescale
 //                            skipping" with threshold 0, :466-487, generalised)
 //   O_t += P_t V_j           tcgen05.mma, A from TMEM, B = V_j as an MN-major operand

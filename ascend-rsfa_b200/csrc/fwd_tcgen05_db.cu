@@ -373,7 +373,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         // such a row keeps its reference max (moving it towards 0 could underflow l).
         const bool nothing_visible = (mb == -INFINITY);
 
-        // Lazy rescale: the reference max moves only when the row max grew by more than 2^8 (the
+        // Lazy rescale: the reference max moves only when the row max grew by more than 2^13 (the
         // reference's threshold-0 "rescale skipping", :466-487, generalised).
         float alpha = 1.f;
         bool grow = false;
@@ -401,7 +401,6 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
 #pragma unroll
             for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
             tmem_st_x32(tO + c0, o);
-            tmem_wait_st();
           }
         }
         RSFA_TRACE_EV(0x3000 + j);   // max done

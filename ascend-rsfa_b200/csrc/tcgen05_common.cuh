@@ -12,7 +12,14 @@ namespace rsfa {
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifndef RSFA_RESCALE_THRESHOLD
+#define RSFA_RESCALE_THRESHOLD 13.0f
+#endif
+// Lazy rescale: the reference max of a row moves only when the row max grew by more than this many
+// log2 units, so P stays <= 2^13 (fp16 holds 2^16; l and O accumulate in fp32).  With peaked
+// softmax rows (BASELINE cfg2: N(0,1) inputs, sm_scale 0.5) a threshold of 8 still rescaled O in
+// TMEM on most early tiles: 13 is worth +3 % non-causal and +10 % causal there.
+constexpr float kRescaleThreshold = RSFA_RESCALE_THRESHOLD;
 
 // Wait-site tags (reported in the status word when a wait runs out).
 enum : int {
