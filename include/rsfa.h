@@ -76,7 +76,8 @@ RSFA_API int rsfa_fwd(const void* q, const void* k, const void* v, void* o, floa
  * streams, and returns when o_host (and lse_host, if not NULL) is complete.  This is the call the
  * reference's harness makes when its tensors start on the host: tensor creation + attention() +
  * synchronize (benchmarks/run_final_benchmark.py:104-124).  Buffers may be pageable; pinned
- * buffers copy faster.  `device` is the CUDA ordinal to use.
+ * buffers copy faster.  `device` is the CUDA ordinal to use.  Calls for one device share its staging
+ * buffers and streams: issue them one at a time per device (different devices are independent).
  */
 RSFA_API int rsfa_fwd_host(const void* q_host, const void* k_host, const void* v_host, void* o_host,
                   float* lse_host, int B, int H, int S, int D, int causal, float sm_scale,

@@ -237,6 +237,28 @@ def test_host_buffer_entry_point(fa, cuda_device):
     assert m["finite"] and m["allclose"], m
 
 
+def test_host_buffer_entry_point_with_lse(fa, cuda_device):
+    """rsfa_fwd_host through ctypes, with the log-sum-exp copied back as well."""
+    from ascend_rsfa import _capi
+
+    lib = _capi.load()
+    B, H, S, D = 2, 3, 320, 128
+    q, k, v = make_inputs(B, H, S, D, seed=16)
+    o = torch.empty_like(q)
+    lse = torch.empty(B, H, S, dtype=torch.float32)
+    fa.set_option("host_slab_heads", 4)
+    try:
+        rc = lib.rsfa_fwd_host(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, H, S, D, 1,
+                               0.2, 128, 128, _capi.RSFA_DTYPE_F16, 0)
+    finally:
+        fa.set_option("host_slab_heads", 0)
+    assert rc == _capi.RSFA_OK, _capi.strerror(rc)
+    ref, lse_ref = attention_fp32(q, k, v, True, 0.2, return_lse=True)
+    m = error_metrics(o, ref)
+    assert m["finite"] and m["allclose"], m
+    assert torch.allclose(lse, lse_ref, atol=2e-3, rtol=2e-3)
+
+
 def test_device_argument_errors(fa, cuda_device):
     q = torch.zeros(1, 1, 128, 64, dtype=torch.float16, device=cuda_device)
     with pytest.raises(ValueError):

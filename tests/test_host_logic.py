@@ -107,3 +107,17 @@ def test_shard_is_a_view():
     assert s.shape == (1, 2, 3, 8) and s.data_ptr() == t.reshape(1, 8, 3, 8)[:, 2:].data_ptr()
     with pytest.raises(ValueError):
         sharding.head_slab(8, 4, 4)
+
+
+def test_tile_table_is_total_and_consistent():
+    """Every (S, D, causal) on the tcgen05 path resolves to an instantiated tile, bucket edges included."""
+    for D in (64, 128, 256):
+        for causal in (False, True):
+            for S in (129, 130, 767, 768, 1535, 1536, 2048, 3071, 3072, 6143, 6144, 8192, 65536, 1 << 20):
+                bm, bn = fa.get_tiling(2, 3, S, D, causal)
+                assert bm == 128 and bn in ((64,) if D == 256 else (64, 128)), (S, D, causal, bm, bn)
+                assert fa.select_path(S, D, causal, 0.1, bm, bn) == (1, bm, bn)
+    for D in (16, 32):
+        assert fa.get_tiling(1, 1, 4096, D, True) == (64, 64)      # generic kernel only
+    for S in (1, 64, 128):
+        assert fa.get_tiling(1, 1, S, 128, False) == (64, 64)      # short-sequence path
