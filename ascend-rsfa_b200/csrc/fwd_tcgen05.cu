@@ -22,11 +22,14 @@
 //                between warpgroups with setmaxnreg (softmax threads keep a whole row in registers)
 // Per key tile j and Q tile t:
 //   S_t = Q_t K_j^T          tcgen05.mma, both operands from shared memory
-//   softmax group t          tcgen05.ld S_t -> running max, exp2, row sum -> P_t
-//                            (16-bit) written back over S_t with tcgen05.st; when a
-//                            row's max grew by more than 2^13 the group rescales its
-//                            O_t rows in TMEM first (the reference's "rescale
-//                            skipping" with threshold 0, :466-487, generalised)
+//   softmax group t          tcgen05.ld S_t -> exp2 against the row's reference (set
+//                            from the first key tile, with headroom), row sum -> P_t
+//                            (16-bit) written back over S_t with tcgen05.st.  No row
+//                            maximum per tile: a warp whose sum check says a P value
+//                            might overflow redoes that tile in a careful path that
+//                            moves the reference and rescales its O_t rows in TMEM
+//                            (the reference's "rescale skipping", :466-487, taken to
+//                            "rescale only when it must")
 //   O_t += P_t V_j           tcgen05.mma, A from TMEM, B = V_j as an MN-major operand
 // The two Q tiles alternate on the tensor pipe, so the MMAs of one overlap the
 // softmax of the other.  TMEM columns: S_0 [0,128)  S_1 [128,256)  O_0 [256,256+D)
@@ -65,7 +68,7 @@ struct Cfg {
   static constexpr int kQBoxBytes = kTileM * 128;             // 128 rows x 128 B
   static constexpr int kKvBoxBytes = kTileN * 128;
   static constexpr int kStageBytes = kTileM * 128;            // epilogue staging: 128 rows x 64 columns
-  static constexpr int kNumBarriers = 2 * kNT + 2 * kStages + 5 * kNT + 4;
+  static constexpr int kNumBarriers = 2 * kNT + 2 * kStages + 6 * kNT + 4;
   static constexpr int kSmemBytes = kNT * kQTileBytes + kStages * kKvTileBytes + kNT * kStageBytes + 1024 /*align*/ +
                                     kNumBarriers * 8 + 64;
   __host__ __device__ static constexpr int kColS(int t) { return t * kTileN; }
@@ -77,6 +80,78 @@ __device__ __forceinline__ int num_kv_tiles(int row0, int S, int causal) {
   if (row0 >= S) return 0;
   const int last_key = causal ? min(S, row0 + kTileM) : S;  // exclusive
   return (last_key + kTileN - 1) / kTileN;
+}
+
+// Careful version of one 64-key half of a softmax step, used once the fast loop's sum check has said
+// that a P value might leave the 16-bit range.  It is deliberately NOT inlined and is called only
+// from the careful loop behind the fast one: inside the fast loop even a call to it slowed every
+// step by 5 %.
+// The scores of the half are still intact in tensor memory (P has not been written over them), so
+// they are loaded again: true row maximum, new reference (with headroom) for rows that exceeded
+// the old one, l and (if `rescale`) this thread's row of O_t brought to the new reference, then
+// exp2 / sum / pack and the tcgen05.st of P.  Returns {new reference, l + this half's sum}.
+// `limit` = last visible score of the half (63 if none is masked).  All 32 lanes call it together.
+template <int D, bool kBf16>
+__device__ __noinline__ uint64_t softmax_half_careful(uint32_t t_s, uint32_t t_p, uint32_t t_o, int limit,
+                                                      float scale_log2, float headroom, float m_used, float l,
+                                                      int rescale) {
+  uint32_t a[32], b[32];
+  tmem_ld_x32(t_s, a);
+  tmem_ld_x32(t_s + 32, b);
+  tmem_wait_ld();
+  reg_fence_x32(a);
+  reg_fence_x32(b);
+  if (limit < 63) {
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      if (c > limit) a[c] = 0xff800000u;
+      if (c + 32 > limit) b[c] = 0xff800000u;
+    }
+  }
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int c = 0; c < 32; c += 4) {
+    mx[0] = max3(mx[0], __uint_as_float(a[c]), __uint_as_float(a[c + 1]));
+    mx[1] = max3(mx[1], __uint_as_float(a[c + 2]), __uint_as_float(a[c + 3]));
+    mx[2] = max3(mx[2], __uint_as_float(b[c]), __uint_as_float(b[c + 1]));
+    mx[3] = max3(mx[3], __uint_as_float(b[c + 2]), __uint_as_float(b[c + 3]));
+  }
+  const float mb = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+  float alpha = 1.f;
+  if (mb > m_used) {
+    const float m_new = mb + headroom;
+    alpha = ex2((m_used - m_new) * scale_log2);
+    l *= alpha;
+    m_used = m_new;
+  }
+  if (rescale && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      uint32_t o[32];
+      tmem_ld_x32(t_o + c0, o);
+      tmem_wait_ld();
+      reg_fence_x32(o);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+      tmem_st_x32(t_o + c0, o);
+    }
+  }
+  const float neg_m = -m_used * scale_log2;
+  float h0 = 0.f, h1 = 0.f;
+  uint32_t pk[32];
+#pragma unroll
+  for (int c = 0; c < 32; c += 2) {
+    const float e0 = ex2(fmaf(__uint_as_float(a[c]), scale_log2, neg_m));
+    const float e1 = ex2(fmaf(__uint_as_float(a[c + 1]), scale_log2, neg_m));
+    const float e2 = ex2(fmaf(__uint_as_float(b[c]), scale_log2, neg_m));
+    const float e3 = ex2(fmaf(__uint_as_float(b[c + 1]), scale_log2, neg_m));
+    h0 += e0 + e1;
+    h1 += e2 + e3;
+    pk[c >> 1] = pack2<kBf16>(e0, e1);
+    pk[16 + (c >> 1)] = pack2<kBf16>(e2, e3);
+  }
+  tmem_st_x32(t_p, pk);
+  return pack_f32x2(m_used, l + (h0 + h1));
 }
 
 template <int D, bool kBf16>
@@ -100,7 +175,9 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   auto bar_p_full = [&](int t, int half) { return sBar + 8u * (3 * kNT + 2 * C::kStages + 2 * t + half); };
   auto bar_o_full = [&](int t) { return sBar + 8u * (5 * kNT + 2 * C::kStages + t); };
   auto bar_epi = [&](int t) { return sBar + 8u * (6 * kNT + 2 * C::kStages + t); };   // group-wide sync of the epilogue
-  const uint32_t bar_sched_full0 = sBar + 8u * (7 * kNT + 2 * C::kStages);  // 2 slots
+  // completion of the PV MMAs of a tile's first 64 keys (waited on only by the softmax slow path)
+  auto bar_pv0_done = [&](int t) { return sBar + 8u * (7 * kNT + 2 * C::kStages + t); };
+  const uint32_t bar_sched_full0 = sBar + 8u * (8 * kNT + 2 * C::kStages);  // 2 slots
   const uint32_t bar_sched_empty0 = bar_sched_full0 + 16u;                   // 2 slots
   const uint32_t misc = sBar + 8u * C::kNumBarriers;
   // misc words: [0] TMEM base, [1] abort flag, [2..3] scheduler ring
@@ -123,6 +200,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       mbar_init(bar_p_full(t, 1), kTileM);
       mbar_init(bar_o_full(t), 1);
       mbar_init(bar_epi(t), kTileM);
+      mbar_init(bar_pv0_done(t), 1);
     }
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_kv_full(s), 1);
@@ -318,6 +396,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
               tc_fence_after_sync();
               RSFA_TRACE_EV(0x1000 + (t << 8) + j);   // P half 0 seen
               issue_pv(t, vidx % C::kStages, j > 0, 0, kTileN / 32);
+              umma_commit_elect(bar_pv0_done(t));
               RSFA_TRACE_EV(0x2000 + (t << 8) + j);   // PV half 0 issued
               ok = wait_all(bar_p_full(t, 1), p_count[t] & 1, kTagPFull);
               if (!ok) break;
@@ -335,9 +414,11 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
                 tc_fence_after_sync();
                 k_ready = true;
               }
+              RSFA_TRACE_EV(0x9000 + (t << 8) + j);   // K ready
               issue_qk(t, kidx % C::kStages);
-              umma_commit_elect(bar_s_full(t));
               RSFA_TRACE_EV(0x5000 + (t << 8) + j);   // QK(j+1) issued
+              umma_commit_elect(bar_s_full(t));
+              RSFA_TRACE_EV(0x8000 + (t << 8) + j);   // S commit issued
               if (j + 2 == n[t]) umma_commit_elect(bar_q_empty(t));
             }
           }
@@ -350,6 +431,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
             }
             umma_commit_elect(bar_kv_empty(kidx % C::kStages));
           }
+          RSFA_TRACE_EV(0x7000 + j);   // iteration end
         }
         if (!ok) break;
         kv_count += 2 * nmax;
@@ -366,11 +448,12 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
     const uint32_t tS = tmem_base + lane_base + C::kColS(t);
     const uint32_t tO = tmem_base + lane_base + C::kColO(t);
     const float scale_log2 = p.sm_scale * kLog2e;
+    const float headroom = kHeadroomLog2 / scale_log2;   // in raw score units (sm_scale > 0 on this path)
     uint32_t item_count = 0, s_count = 0, o_count = 0, epi_count = 0;
     bool ok = true;
 #ifdef RSFA_TRACE
-    unsigned long long* trace_buf = (p.trace != nullptr && blockIdx.x == 0 && (warp & 3) == 0 && lane == 0)
-                                        ? p.trace + t * 2 * kTraceCap : nullptr;
+    unsigned long long* trace_buf = (p.trace != nullptr && blockIdx.x == 0 && lane == 0)
+                                        ? p.trace + ((warp & 3) == 0 ? t : 4 + warp) * 2 * kTraceCap : nullptr;
     int trace_n = 0;
 #endif
     while (ok) {
@@ -390,9 +473,20 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       const int n_tiles = num_kv_tiles(tile_row0, S, p.causal);
       if (n_tiles == 0) continue;
 
-      float m_used = -INFINITY;  // reference max, in raw score units
+      // The reference maximum m_used of a row is set from the first key tile (plus headroom) and is
+      // NOT recomputed per tile: a tile is exponentiated against the current reference straight
+      // away.  Only when the sum of a 64-key half exceeds kSumLimit (every P value of the half is
+      // bounded by that sum, so none can have left the 16-bit range otherwise) does the warp leave
+      // this loop and finish the work item in the careful loop below, which redoes that half and
+      // handles the remaining key tiles with a row maximum per half.  This replaces the per-tile
+      // maximum of the reference's loop (:196-203) and its "rescale only when the maximum moved"
+      // (:466-487) by "rescale only when it must".
+      float m_used = -INFINITY;  // reference, in raw score units
       float l = 0.f;
-      for (int j = 0; j < n_tiles; ++j) {
+      int j = 0;
+      while (j < n_tiles) {
+      int careful_half = -1;     // >= 0: the half of key tile j that failed the check
+      for (; j < n_tiles; ++j) {
         ok = mbar_wait(bar_s_full(t), s_count & 1, abort_flag, wait_ns, kTagSFull);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -411,10 +505,6 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         reg_fence_x32(s2);
         reg_fence_x32(s3);
         RSFA_TRACE_EV(0x2000 + j);   // S in registers
-#ifdef RSFA_TRACE
-        { uint32_t tmp; asm volatile("mov.b32 %0, %1;" : "=r"(tmp) : "r"(s0[0])); RSFA_TRACE_EV(0x8000 + j);
-          asm volatile("mov.b32 %0, %1;" : "=r"(tmp) : "r"(s3[31])); RSFA_TRACE_EV(0x9000 + j); }
-#endif
 
         // masked tile: the one crossing the diagonal, or the ragged end of the sequence
         const int n0 = j * kTileN;
@@ -431,8 +521,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
             if (c + 96 > limit) s3[c] = ninf;
           }
         }
-        float mb;
-        {
+        if (j == 0) {
           float mx[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
@@ -447,43 +536,15 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
             mx[6] = max3(mx[6], __uint_as_float(s3[c]), __uint_as_float(s3[c + 1]));
             mx[7] = max3(mx[7], __uint_as_float(s3[c + 2]), __uint_as_float(s3[c + 3]));
           }
-          mb = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
+          float mb = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
+          if (mb == -INFINITY) mb = 0.f;  // only rows past S can get here; keep them finite
+          m_used = mb + headroom;
         }
-        if (mb == -INFINITY) mb = 0.f;  // only rows past S can get here; keep them finite
-#ifdef RSFA_TRACE
-        { uint32_t tmp; asm volatile("mov.b32 %0, %1;" : "=r"(tmp) : "r"(__float_as_uint(mb))); RSFA_TRACE_EV(0xa000 + j); }
-#endif
-
-        // Lazy rescale: move the reference max only when it grew by more than the threshold.
-        float alpha = 1.f;
-        bool grow = false;
-        if (j == 0) {
-          m_used = mb;
-        } else if ((mb - m_used) * scale_log2 > kRescaleThreshold) {
-          alpha = ex2((m_used - mb) * scale_log2);
-          l *= alpha;
-          m_used = mb;
-          grow = true;
-        }
-        if (__any_sync(0xffffffffu, grow)) {
-          // O_t is quiescent here: S_t(j) complete implies every earlier MMA of this tile completed.
-#pragma unroll 1
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t o[32];
-            tmem_ld_x32(tO + c0, o);
-            tmem_wait_ld();
-            reg_fence_x32(o);
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-            tmem_st_x32(tO + c0, o);
-          }
-        }
-
-        RSFA_TRACE_EV(0x3000 + j);   // max done
+        RSFA_TRACE_EV(0x3000 + j);   // reference ready
         const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
         const float neg_m = -m_used * scale_log2;
         const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
-        uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
+        uint64_t sum_a, sum_b;
         // exp2, row sum and 16-bit packing of 32 scores into pk[base .. base+16).  The packed
         // values of one half (64 keys) are collected first and stored with a single tcgen05.st:
         // a store issued per 32 scores would make the next chunk's arithmetic wait on it, because
@@ -503,10 +564,24 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
             pk[base + (c >> 1) + 1] = pack2<kBf16>(e2, e3);
           }
         };
+        auto exp_half = [&](uint32_t (&sa)[32], uint32_t (&sb)[32], uint32_t (&pk)[32]) -> float {
+          sum_a = pack_f32x2(0.f, 0.f);
+          sum_b = sum_a;
+          exp_pack(sa, pk, 0);
+          exp_pack(sb, pk, 16);
+          float a0, a1;
+          unpack_f32x2(add_f32x2(sum_a, sum_b), a0, a1);
+          return a0 + a1;
+        };
         {
           uint32_t pk[32];
-          exp_pack(s0, pk, 0);
-          exp_pack(s1, pk, 16);
+          const float h = exp_half(s0, s1, pk);
+          // !(h <= limit) also catches NaN and +inf.  Nothing of this half has been stored yet.
+          if (__any_sync(0xffffffffu, !(h <= kSumLimit))) {
+            careful_half = 0;
+            break;
+          }
+          l += h;
           RSFA_TRACE_EV(0xb000);   // half 0 computed
           tmem_st_x32(tS, pk);
           tmem_wait_st();
@@ -516,20 +591,49 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         }
         {
           uint32_t pk[32];
-          exp_pack(s2, pk, 0);
-          exp_pack(s3, pk, 16);
+          const float h = exp_half(s2, s3, pk);
+          if (__any_sync(0xffffffffu, !(h <= kSumLimit))) {
+            careful_half = 1;
+            break;
+          }
+          l += h;
           RSFA_TRACE_EV(0xb001);   // half 1 computed
           tmem_st_x32(tS + 32, pk);
-          {
-            float a0, a1;
-            unpack_f32x2(add_f32x2(sum_a, sum_b), a0, a1);
-            l += a0 + a1;
-          }
           tmem_wait_st();
           tc_fence_before_sync();
           mbar_arrive(bar_p_full(t, 1));
         }
         RSFA_TRACE_EV(0x5000 + j);   // half 1 handed over
+      }
+      if (!ok) break;
+      if (careful_half >= 0) {
+        // Finish key tile j half by half with the scores loaded again from tensor memory (P has
+        // not been written over the half that failed the check, nor over the one behind it), then
+        // go back to the fast loop.  The PV MMAs of the tile's first half accumulate into O_t, so
+        // the second half waits for them before it may rescale O_t.
+        RSFA_TRACE_EV(0xc000 + j);
+        const int n0 = j * kTileN;
+        int limit = S - 1 - n0;                             // last visible column of this tile
+        if (p.causal) limit = min(limit, row - n0);
+        for (int half = careful_half; half < 2; ++half) {
+          if (half == 1) {
+            ok = mbar_wait(bar_pv0_done(t), (s_count - 1) & 1, abort_flag, wait_ns, kTagPvDone);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+          }
+          // half 0: O_t is quiescent, S_t(j) complete implies every earlier MMA of this tile completed
+          const uint64_t r = softmax_half_careful<D, kBf16>(tS + 64 * half, tS + 32 * half, tO, limit - 64 * half,
+                                                            scale_log2, headroom, m_used, l,
+                                                            (j > 0 || half > 0) ? 1 : 0);
+          unpack_f32x2(r, m_used, l);
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(bar_p_full(t, half));
+        }
+        if (!ok) break;
+        ++j;
+      }
       }
       if (!ok) break;
 

@@ -20,10 +20,28 @@ constexpr float kLog2e = 1.4426950408889634f;
 // softmax rows (BASELINE cfg2: N(0,1) inputs, sm_scale 0.5) a threshold of 8 still rescaled O in
 // TMEM on most early tiles: 13 is worth +3 % non-causal and +10 % causal there.
 constexpr float kRescaleThreshold = RSFA_RESCALE_THRESHOLD;
+#ifndef RSFA_SUM_LIMIT
+#define RSFA_SUM_LIMIT 32768.0f
+#endif
+#ifndef RSFA_HEADROOM
+#define RSFA_HEADROOM 6.0f
+#endif
+// The reference maximum of a row is placed this many log2 units ABOVE the largest score seen when
+// it is set, so P starts at <= 2^-6 and a row can grow by 21 log2 units before anything has to be
+// rescaled.  fp16 keeps full precision down to 2^-14, i.e. for weights down to 2^-8 of the row's
+// largest, and denormals (absolute error 2^-19 of the largest weight) below that.  On BASELINE
+// cfg2 (N(0,1) inputs, sm_scale 0.5: near one-hot rows) 0.6 % of the warp-steps still took the
+// careful path with a headroom of 4; 4 -> 6 -> 8 gave 1171 -> 1194 -> 1206 TFLOP/s there.
+constexpr float kHeadroomLog2 = RSFA_HEADROOM;
+// Bound on the sum of the exponentials of one 64-key half of a row (and thereby on every P value
+// of it; all terms are non-negative) above which the softmax leaves its fast path; fp16 holds
+// 65504.
+constexpr float kSumLimit = RSFA_SUM_LIMIT;
 
 // Wait-site tags (reported in the status word when a wait runs out).
 enum : int {
-  kTagQEmpty = 1, kTagKvEmpty, kTagQFull, kTagKvFull, kTagPFull, kTagSFull, kTagOFull, kTagSched, kTagEpilogue
+  kTagQEmpty = 1, kTagKvEmpty, kTagQFull, kTagKvFull, kTagPFull, kTagSFull, kTagOFull, kTagSched, kTagEpilogue,
+  kTagPvDone
 };
 
 // Debug builds (-DRSFA_TRACE) log (clock, code) pairs per role for CTA 0; the product build

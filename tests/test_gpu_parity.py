@@ -164,6 +164,31 @@ def test_wide_logits_online_softmax_stability(fa, cuda_device):
 
 
 @pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("tile", [(128, 128), (128, 64)])
+@pytest.mark.parametrize("D", [64, 128])
+def test_sudden_growth_of_the_row_maximum(fa, cuda_device, causal, tile, D):
+    # The kernels exponentiate a key tile against a reference fixed at the first tile and move
+    # it only when a value might leave the 16-bit range of P.  Flat scores everywhere except a
+    # few keys that beat everything before them by far more than that range: one in the second
+    # half of a tile, one in the first half of a later tile, one in the last (diagonal) tile.
+    B, H, S = 1, 2, 640
+    g = torch.Generator().manual_seed(21)
+    u = torch.ones(D) / math.sqrt(D)
+    q = (0.3 * torch.randn(B, H, S, D, generator=g) + 2.0 * u).half()
+    k = (0.3 * torch.randn(B, H, S, D, generator=g)).half()
+    v = torch.randn(B, H, S, D, generator=g).half()
+    for idx, c in ((128 + 70, 40.0), (256 + 10, 90.0), (512 + 100, 150.0)):
+        k[:, :, idx, :] = (c * u).half()
+    m = check(fa, q, k, v, causal, 0.5, tile[0], tile[1], cuda_device)
+    assert m["max_abs"] < 4e-3, m
+    # moderate growth (a few log2 units per tile) must stay on the fast path and stay exact too
+    k2 = (0.3 * torch.randn(B, H, S, D, generator=g)).half()
+    k2 *= torch.linspace(0.5, 3.0, S)[None, None, :, None].half()
+    m = check(fa, q, k2, v, causal, 0.5, tile[0], tile[1], cuda_device)
+    assert m["max_abs"] < 4e-3, m
+
+
+@pytest.mark.parametrize("causal", [False, True])
 def test_head_dim_256_shapes(fa, cuda_device, causal):
     # cfg3's per-head shape (S=1024, D=256, sm_scale=1/16) on a few heads, plus forced rescales
     q, k, v = make_inputs(2, 3, 1024, 256, seed=12)
