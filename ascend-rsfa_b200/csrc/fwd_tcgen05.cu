@@ -82,78 +82,6 @@ __device__ __forceinline__ int num_kv_tiles(int row0, int S, int causal) {
   return (last_key + kTileN - 1) / kTileN;
 }
 
-// Careful version of one 64-key half of a softmax step, used once the fast loop's sum check has said
-// that a P value might leave the 16-bit range.  It is deliberately NOT inlined and is called only
-// from the careful loop behind the fast one: inside the fast loop even a call to it slowed every
-// step by 5 %.
-// The scores of the half are still intact in tensor memory (P has not been written over them), so
-// they are loaded again: true row maximum, new reference (with headroom) for rows that exceeded
-// the old one, l and (if `rescale`) this thread's row of O_t brought to the new reference, then
-// exp2 / sum / pack and the tcgen05.st of P.  Returns {new reference, l + this half's sum}.
-// `limit` = last visible score of the half (63 if none is masked).  All 32 lanes call it together.
-template <int D, bool kBf16>
-__device__ __noinline__ uint64_t softmax_half_careful(uint32_t t_s, uint32_t t_p, uint32_t t_o, int limit,
-                                                      float scale_log2, float headroom, float m_used, float l,
-                                                      int rescale) {
-  uint32_t a[32], b[32];
-  tmem_ld_x32(t_s, a);
-  tmem_ld_x32(t_s + 32, b);
-  tmem_wait_ld();
-  reg_fence_x32(a);
-  reg_fence_x32(b);
-  if (limit < 63) {
-#pragma unroll
-    for (int c = 0; c < 32; ++c) {
-      if (c > limit) a[c] = 0xff800000u;
-      if (c + 32 > limit) b[c] = 0xff800000u;
-    }
-  }
-  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-  for (int c = 0; c < 32; c += 4) {
-    mx[0] = max3(mx[0], __uint_as_float(a[c]), __uint_as_float(a[c + 1]));
-    mx[1] = max3(mx[1], __uint_as_float(a[c + 2]), __uint_as_float(a[c + 3]));
-    mx[2] = max3(mx[2], __uint_as_float(b[c]), __uint_as_float(b[c + 1]));
-    mx[3] = max3(mx[3], __uint_as_float(b[c + 2]), __uint_as_float(b[c + 3]));
-  }
-  const float mb = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-  float alpha = 1.f;
-  if (mb > m_used) {
-    const float m_new = mb + headroom;
-    alpha = ex2((m_used - m_new) * scale_log2);
-    l *= alpha;
-    m_used = m_new;
-  }
-  if (rescale && __any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-    for (int c0 = 0; c0 < D; c0 += 32) {
-      uint32_t o[32];
-      tmem_ld_x32(t_o + c0, o);
-      tmem_wait_ld();
-      reg_fence_x32(o);
-#pragma unroll
-      for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-      tmem_st_x32(t_o + c0, o);
-    }
-  }
-  const float neg_m = -m_used * scale_log2;
-  float h0 = 0.f, h1 = 0.f;
-  uint32_t pk[32];
-#pragma unroll
-  for (int c = 0; c < 32; c += 2) {
-    const float e0 = ex2(fmaf(__uint_as_float(a[c]), scale_log2, neg_m));
-    const float e1 = ex2(fmaf(__uint_as_float(a[c + 1]), scale_log2, neg_m));
-    const float e2 = ex2(fmaf(__uint_as_float(b[c]), scale_log2, neg_m));
-    const float e3 = ex2(fmaf(__uint_as_float(b[c + 1]), scale_log2, neg_m));
-    h0 += e0 + e1;
-    h1 += e2 + e3;
-    pk[c >> 1] = pack2<kBf16>(e0, e1);
-    pk[16 + (c >> 1)] = pack2<kBf16>(e2, e3);
-  }
-  tmem_st_x32(t_p, pk);
-  return pack_f32x2(m_used, l + (h0 + h1));
-}
-
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, const SchedInfo sched) {
@@ -174,7 +102,6 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   // P_t is handed to the MMA warp in two halves of 64 keys so the first PV MMAs start early.
   auto bar_p_full = [&](int t, int half) { return sBar + 8u * (3 * kNT + 2 * C::kStages + 2 * t + half); };
   auto bar_o_full = [&](int t) { return sBar + 8u * (5 * kNT + 2 * C::kStages + t); };
-  auto bar_epi = [&](int t) { return sBar + 8u * (6 * kNT + 2 * C::kStages + t); };   // group-wide sync of the epilogue
   // completion of the PV MMAs of a tile's first 64 keys (waited on only by the softmax slow path)
   auto bar_pv0_done = [&](int t) { return sBar + 8u * (7 * kNT + 2 * C::kStages + t); };
   const uint32_t bar_sched_full0 = sBar + 8u * (8 * kNT + 2 * C::kStages);  // 2 slots
@@ -199,7 +126,6 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       mbar_init(bar_p_full(t, 0), kTileM);
       mbar_init(bar_p_full(t, 1), kTileM);
       mbar_init(bar_o_full(t), 1);
-      mbar_init(bar_epi(t), kTileM);
       mbar_init(bar_pv0_done(t), 1);
     }
     for (int s = 0; s < C::kStages; ++s) {
@@ -329,6 +255,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_sched_empty0 + 8u * slot);
         if (item >= sched.total_items) break;
+        RSFA_TRACE_EV(0xa000);   // item known
         int bh, row0;
         decode(item, bh, row0);
         int n[kNT];
@@ -366,11 +293,13 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         for (int t = 0; ok && t < kNT; ++t)
           ok = wait_all(bar_q_full(t), item_count & 1, kTagQFull);
         if (!ok) break;
+        RSFA_TRACE_EV(0xa100);   // Q present
         const uint32_t base = kv_count;  // K_j at base + 2j, V_j at base + 2j + 1
         if (nmax > 0) {
           ok = wait_kv(base);
           if (!ok) break;
           tc_fence_after_sync();
+          RSFA_TRACE_EV(0xa200);   // K_0 present
           for (int t = 0; t < kNT; ++t) {
             if (n[t] > 0) {
               issue_qk(t, base % C::kStages);
@@ -449,7 +378,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
     const uint32_t tO = tmem_base + lane_base + C::kColO(t);
     const float scale_log2 = p.sm_scale * kLog2e;
     const float headroom = kHeadroomLog2 / scale_log2;   // in raw score units (sm_scale > 0 on this path)
-    uint32_t item_count = 0, s_count = 0, o_count = 0, epi_count = 0;
+    uint32_t item_count = 0, s_count = 0, o_count = 0;
     bool ok = true;
 #ifdef RSFA_TRACE
     unsigned long long* trace_buf = (p.trace != nullptr && blockIdx.x == 0 && lane == 0)
@@ -646,17 +575,15 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       RSFA_TRACE_EV(0x6000);         // O complete seen
       const float inv_l = 1.f / l;
       const int b = bh / p.H, h = bh - b * p.H;
-      // O_t / l goes to global memory through a 128-byte-swizzled staging buffer and one TMA store
-      // per 64 columns: a thread owns a whole row, so direct stores would touch 32 different
-      // lines per instruction.  Rows past S are clipped by the TMA store.
-      const uint32_t stage = sStage + t * C::kStageBytes;
-      const bool issuer = (row_in_tile == 0);
-      auto group_sync = [&]() -> bool {
-        mbar_arrive(bar_epi(t));
-        bool r = mbar_wait(bar_epi(t), epi_count & 1, abort_flag, wait_ns, kTagEpilogue);
-        ++epi_count;
-        return __all_sync(0xffffffffu, r) != 0;
-      };
+      // O_t / l goes to global memory through 128-byte-swizzled staging and TMA stores: a thread
+      // owns a whole row, so direct stores would touch 32 different lines per instruction.  Each
+      // warp stages and stores its own 32 rows (one box of 64 columns at a time), so the epilogue
+      // needs no synchronisation wider than a warp.  Rows past S are clipped by the TMA store; a
+      // warp whose rows all lie past S stores nothing.
+      const int wq = warp & 3;
+      const uint32_t stage = sStage + t * C::kStageBytes + wq * 4096;
+      const bool issuer = (lane == 0);
+      const bool any_row = (tile_row0 + wq * 32 < S);
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 64) {
         uint32_t o0[32], o1[32];
@@ -665,11 +592,10 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         tmem_wait_ld();
         reg_fence_x32(o0);
         reg_fence_x32(o1);
-        if (issuer) tma_store_wait_read();   // the previous store no longer reads the staging buffer
-        ok = group_sync();
-        if (!ok) break;
-        const uint32_t row_addr = stage + row_in_tile * 128;
-        const uint32_t sw = static_cast<uint32_t>(row_in_tile & 7);
+        if (issuer) tma_store_wait_read();   // this warp's previous store no longer reads its staging rows
+        __syncwarp();
+        const uint32_t row_addr = stage + lane * 128;
+        const uint32_t sw = static_cast<uint32_t>(lane & 7);
 #pragma unroll
         for (int c = 0; c < 32; c += 8) {
           st_shared_v4(row_addr + (((c >> 3) ^ sw) << 4),
@@ -684,20 +610,18 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
                        pack2<kBf16>(__uint_as_float(o1[c + 6]) * inv_l, __uint_as_float(o1[c + 7]) * inv_l));
         }
         fence_proxy_async();
-        ok = group_sync();
-        if (!ok) break;
-        if (issuer) {
-          tma_store_4d(&maps.o, stage, c0, tile_row0, h, b);
+        __syncwarp();
+        if (issuer && any_row) {
+          tma_store_4d(&maps.o, stage, c0, tile_row0 + wq * 32, h, b);
           tma_store_commit();
         }
       }
-      if (!ok) break;
       if (p.lse != nullptr && row < S)
         p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);
       tc_fence_before_sync();
       RSFA_TRACE_EV(0x7000);         // epilogue done
     }
-    if (row_in_tile == 0) tma_store_wait_all();   // the last TMA stores must be complete before the CTA exits
+    if (lane == 0) tma_store_wait_all();   // the last TMA stores must be complete before the CTA exits
   }
 
   // ------------------------------------------------------------------ teardown
@@ -719,7 +643,7 @@ cudaError_t launch_one(const FwdParams& p, int sm_count, cudaStream_t stream, lo
   using C = Cfg<D>;
   TmaMaps maps;
   if (!make_map(&maps.q, p.q, p, p.q_stride, kTileM) || !make_map(&maps.k, p.k, p, p.k_stride, kTileN) ||
-      !make_map(&maps.v, p.v, p, p.v_stride, kTileN) || !make_map(&maps.o, p.o, p, p.o_stride, kTileM))
+      !make_map(&maps.v, p.v, p, p.v_stride, kTileN) || !make_map(&maps.o, p.o, p, p.o_stride, 32))
     return cudaErrorInvalidValue;
   SchedInfo sched;
   sched.items_per_head = (p.S + kNT * kTileM - 1) / (kNT * kTileM);

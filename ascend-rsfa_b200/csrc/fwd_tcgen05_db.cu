@@ -8,8 +8,10 @@
 // while the softmax warps are still on tile j+1: the softmax -> PV -> QK^T dependency chain of a
 // single-buffered design is cut, the tensor pipe and the softmax warps each run back to back.
 //   S_t[j & 1] = Q_t K_j^T    D/16 MMAs of 128 x 64 x 16, both operands in shared memory
-//   softmax group t           tcgen05.ld S -> mask (diagonal / ragged tiles) -> row max -> lazy
-//                             rescale -> exp2 -> row sum -> P_j (16-bit) over S_t[j & 1]
+//   softmax group t           tcgen05.ld S -> mask (diagonal / ragged tiles) -> exp2 against the
+//                             row's reference -> row sum -> sum check -> P_j (16-bit) over
+//                             S_t[j & 1]; a failed check redoes the tile carefully (new reference,
+//                             rescale of O_t in TMEM)
 //   O_t += P_j V_j            4 MMAs of 128 x D x 16, A = P_j from TMEM, B = V_j MN-major
 // One MMA-issuing warp per Q tile: a wait on an mbarrier costs the issuing warp about 100 cycles
 // even when it is already satisfied and a tcgen05.mma about 40, so one warp cannot feed both tiles.
@@ -72,7 +74,6 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   auto bar_p_full = [&](int t, int b) { return sBar + 8u * (6 * NT + 2 * t + b); };
   auto bar_kv_full = [&](int s) { return sBar + 8u * (8 * NT + s); };
   auto bar_kv_empty = [&](int s) { return sBar + 8u * (8 * NT + C::kStages + s); };
-  auto bar_epi = [&](int t) { return sBar + 8u * (8 * NT + 2 * C::kStages + t); };   // group-wide sync of the epilogue
   const uint32_t bar_sched_full0 = sBar + 8u * (9 * NT + 2 * C::kStages);  // 2 slots
   const uint32_t bar_sched_empty0 = bar_sched_full0 + 16u;                 // 2 slots
   const uint32_t misc = sBar + 8u * C::kNumBarriers;
@@ -92,7 +93,6 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       mbar_init(bar_q_empty(t), 1);
       mbar_init(bar_pv_done(t), 1);
       mbar_init(bar_o_full(t), 1);
-      mbar_init(bar_epi(t), kRowsDb);
       for (int b = 0; b < 2; ++b) {
         mbar_init(bar_s_full(t, b), 1);
         mbar_init(bar_p_full(t, b), kRowsDb);
@@ -300,7 +300,8 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tO = tmem_base + lane_base + C::col_o(t);
     const float scale_log2 = p.sm_scale * kLog2e;
-    uint32_t item_count = 0, o_count = 0, pv_count = 0, epi_count = 0;
+    const float headroom = kHeadroomLog2 / scale_log2;   // in raw score units (sm_scale > 0 on this path)
+    uint32_t item_count = 0, o_count = 0, pv_count = 0;
     uint32_t s_count[2] = {0, 0};
     bool ok = true;
 #ifdef RSFA_TRACE
@@ -325,116 +326,119 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       const int n = num_kv_tiles_db(tile_row0, S, p.causal);
       if (n == 0) continue;
 
-      float m_used = -INFINITY;   // reference max, raw score units
+      // As in the 128-key kernel: the row's reference is set from the first key tile (plus
+      // headroom) and a tile is exponentiated against it straight away; only when the sum check
+      // says that a P value might leave the 16-bit range is that tile redone by
+      // softmax_half_careful, which moves the reference and rescales this thread's row of O_t.
+      float m_used = -INFINITY;   // reference, raw score units
       float l = 0.f;
-      for (int j = 0; j < n; ++j) {
-        const int buf = j & 1;
-        const uint32_t tS = tmem_base + lane_base + C::col_s(t, buf);
-        ok = mbar_wait(bar_s_full(t, buf), s_count[buf] & 1, abort_flag, wait_ns, kTagSFull);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        ++s_count[buf];
-        tc_fence_after_sync();
-        RSFA_TRACE_EV(0x1000 + j);   // S seen
-
-        uint32_t s0[32], s1[32];
-        tmem_ld_x32(tS + 0, s0);
-        tmem_ld_x32(tS + 32, s1);
-        tmem_wait_ld();
-        reg_fence_x32(s0);
-        reg_fence_x32(s1);
-
-        // masked tile: one that crosses the diagonal, or the ragged end of the sequence
-        const int n0 = j * kKeysDb;
-        const bool masked = (n0 + kKeysDb > S) || (p.causal && n0 + kKeysDb > tile_row0 + 1);
-        if (masked) {
-          int limit = S - 1 - n0;   // last visible column of this tile
-          if (p.causal) limit = min(limit, row - n0);
-          const uint32_t ninf = 0xff800000u;
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            if (c > limit) s0[c] = ninf;
-            if (c + 32 > limit) s1[c] = ninf;
-          }
-        }
-        float mb;
-        {
-          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-          for (int c = 0; c < 32; c += 4) {
-            mx[0] = max3(mx[0], __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
-            mx[1] = max3(mx[1], __uint_as_float(s0[c + 2]), __uint_as_float(s0[c + 3]));
-            mx[2] = max3(mx[2], __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
-            mx[3] = max3(mx[3], __uint_as_float(s1[c + 2]), __uint_as_float(s1[c + 3]));
-          }
-          mb = fmaxf(max3(mx[0], mx[1], mx[2]), mx[3]);
-        }
-        // With 64-key tiles the upper rows of a Q tile see nothing of the second diagonal tile:
-        // such a row keeps its reference max (moving it towards 0 could underflow l).
-        const bool nothing_visible = (mb == -INFINITY);
-
-        // Lazy rescale: the reference max moves only when the row max grew by more than 2^13 (the
-        // reference's threshold-0 "rescale skipping", :466-487, generalised).
-        float alpha = 1.f;
-        bool grow = false;
-        if (j == 0) {
-          m_used = nothing_visible ? 0.f : mb;
-        } else if (!nothing_visible && (mb - m_used) * scale_log2 > kRescaleThreshold) {
-          alpha = ex2((m_used - mb) * scale_log2);
-          l *= alpha;
-          m_used = mb;
-          grow = true;
-        }
-        if (__any_sync(0xffffffffu, grow)) {
-          // QK^T of this tile was issued before PV of the previous one, so O_t may still be
-          // written: wait for PV_{j-1} (completion number pv_count + j - 1 of this tile).
-          ok = mbar_wait(bar_pv_done(t), (pv_count + j - 1) & 1, abort_flag, wait_ns, kTagOFull);
+      int j = 0;
+      while (j < n) {
+        bool careful = false;
+        for (; j < n; ++j) {
+          const int buf = j & 1;
+          const uint32_t tS = tmem_base + lane_base + C::col_s(t, buf);
+          ok = mbar_wait(bar_s_full(t, buf), s_count[buf] & 1, abort_flag, wait_ns, kTagSFull);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
+          ++s_count[buf];
           tc_fence_after_sync();
-#pragma unroll 1
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t o[32];
-            tmem_ld_x32(tO + c0, o);
-            tmem_wait_ld();
-            reg_fence_x32(o);
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-            tmem_st_x32(tO + c0, o);
-          }
-        }
-        RSFA_TRACE_EV(0x3000 + j);   // max done
+          RSFA_TRACE_EV(0x1000 + j);   // S seen
 
-        const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
-        const float neg_m = -m_used * scale_log2;
-        const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
-        uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
-        uint32_t pk[32];   // all 64 keys are packed first, then stored with one tcgen05.st
-        auto exp_pack = [&](uint32_t (&sv)[32], int base) {
+          uint32_t s0[32], s1[32];
+          tmem_ld_x32(tS + 0, s0);
+          tmem_ld_x32(tS + 32, s1);
+          tmem_wait_ld();
+          reg_fence_x32(s0);
+          reg_fence_x32(s1);
+
+          // masked tile: one that crosses the diagonal, or the ragged end of the sequence
+          const int n0 = j * kKeysDb;
+          const bool masked = (n0 + kKeysDb > S) || (p.causal && n0 + kKeysDb > tile_row0 + 1);
+          if (masked) {
+            int limit = S - 1 - n0;   // last visible column of this tile
+            if (p.causal) limit = min(limit, row - n0);
+            const uint32_t ninf = 0xff800000u;
 #pragma unroll
-          for (int c = 0; c < 32; c += 4) {
-            float x0, x1, x2, x3;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3])), scale2, neg_m2), x2, x3);
-            const float e0 = ex2(x0), e1 = ex2(x1), e2 = ex2(x2), e3 = ex2(x3);
-            sum_a = add_f32x2(sum_a, pack_f32x2(e0, e1));
-            sum_b = add_f32x2(sum_b, pack_f32x2(e2, e3));
-            pk[base + (c >> 1)] = pack2<kBf16>(e0, e1);
-            pk[base + (c >> 1) + 1] = pack2<kBf16>(e2, e3);
+            for (int c = 0; c < 32; ++c) {
+              if (c > limit) s0[c] = ninf;
+              if (c + 32 > limit) s1[c] = ninf;
+            }
           }
-        };
-        exp_pack(s0, 0);
-        exp_pack(s1, 16);
-        tmem_st_x32(tS, pk);
-        {
+          if (j == 0) {
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 32; c += 4) {
+              mx[0] = max3(mx[0], __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
+              mx[1] = max3(mx[1], __uint_as_float(s0[c + 2]), __uint_as_float(s0[c + 3]));
+              mx[2] = max3(mx[2], __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
+              mx[3] = max3(mx[3], __uint_as_float(s1[c + 2]), __uint_as_float(s1[c + 3]));
+            }
+            float mb = fmaxf(max3(mx[0], mx[1], mx[2]), mx[3]);
+            if (mb == -INFINITY) mb = 0.f;   // only rows past S can get here; keep them finite
+            m_used = mb + headroom;
+          }
+          RSFA_TRACE_EV(0x3000 + j);   // reference ready
+
+          const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
+          const float neg_m = -m_used * scale_log2;
+          const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
+          uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
+          uint32_t pk[32];   // all 64 keys are packed first, then stored with one tcgen05.st
+          auto exp_pack = [&](uint32_t (&sv)[32], int base) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 4) {
+              float x0, x1, x2, x3;
+              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
+              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3])), scale2, neg_m2), x2, x3);
+              const float e0 = ex2(x0), e1 = ex2(x1), e2 = ex2(x2), e3 = ex2(x3);
+              sum_a = add_f32x2(sum_a, pack_f32x2(e0, e1));
+              sum_b = add_f32x2(sum_b, pack_f32x2(e2, e3));
+              pk[base + (c >> 1)] = pack2<kBf16>(e0, e1);
+              pk[base + (c >> 1) + 1] = pack2<kBf16>(e2, e3);
+            }
+          };
+          exp_pack(s0, 0);
+          exp_pack(s1, 16);
           float a0, a1;
           unpack_f32x2(add_f32x2(sum_a, sum_b), a0, a1);
-          l += a0 + a1;
+          const float h = a0 + a1;
+          // !(h <= limit) also catches NaN and +inf.  Nothing of this tile has been stored yet.
+          if (__any_sync(0xffffffffu, !(h <= kSumLimit))) {
+            careful = true;
+            break;
+          }
+          l += h;
+          tmem_st_x32(tS, pk);
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(bar_p_full(t, buf));
+          RSFA_TRACE_EV(0x5000 + j);   // P handed over
         }
-        tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(bar_p_full(t, buf));
-        RSFA_TRACE_EV(0x5000 + j);   // P handed over
+        if (!ok) break;
+        if (careful) {
+          // Redo key tile j with its scores loaded again from tensor memory, then go back to the
+          // fast loop.  QK^T of this tile was issued before PV of the previous one, so O_t may
+          // still be written: wait for PV_{j-1} (completion number pv_count + j - 1 of this tile).
+          const int buf = j & 1;
+          const uint32_t tS = tmem_base + lane_base + C::col_s(t, buf);
+          if (j > 0) {
+            ok = mbar_wait(bar_pv_done(t), (pv_count + j - 1) & 1, abort_flag, wait_ns, kTagOFull);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+          }
+          const int n0 = j * kKeysDb;
+          int limit = S - 1 - n0;
+          if (p.causal) limit = min(limit, row - n0);
+          const uint64_t r = softmax_half_careful<D, kBf16>(tS, tS, tO, limit, scale_log2, headroom, m_used, l,
+                                                            j > 0 ? 1 : 0);
+          unpack_f32x2(r, m_used, l);
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(bar_p_full(t, buf));
+          ++j;
+        }
       }
       if (!ok) break;
       pv_count += n;
@@ -448,17 +452,15 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       RSFA_TRACE_EV(0x6000);   // O seen
       const float inv_l = 1.f / l;
       const int b = bh / p.H, h = bh - b * p.H;
-      // O_t / l goes to global memory through a 128-byte-swizzled staging buffer and one TMA store
-      // per 64 columns: a thread owns a whole row, so direct stores would touch 32 different
-      // lines per instruction.  Rows past S are clipped by the TMA store.
-      const uint32_t stage = sStage + t * C::kStageBytes;
-      const bool issuer = (row_in_tile == 0);
-      auto group_sync = [&]() -> bool {
-        mbar_arrive(bar_epi(t));
-        bool r = mbar_wait(bar_epi(t), epi_count & 1, abort_flag, wait_ns, kTagEpilogue);
-        ++epi_count;
-        return __all_sync(0xffffffffu, r) != 0;
-      };
+      // O_t / l goes to global memory through 128-byte-swizzled staging and TMA stores: a thread
+      // owns a whole row, so direct stores would touch 32 different lines per instruction.  Each
+      // warp stages and stores its own 32 rows (one box of 64 columns at a time), so the epilogue
+      // needs no synchronisation wider than a warp.  Rows past S are clipped by the TMA store; a
+      // warp whose rows all lie past S stores nothing.
+      const int wq = warp & 3;
+      const uint32_t stage = sStage + t * C::kStageBytes + wq * 4096;
+      const bool issuer = (lane == 0);
+      const bool any_row = (tile_row0 + wq * 32 < S);
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 64) {
         uint32_t o0[32], o1[32];
@@ -467,11 +469,10 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         tmem_wait_ld();
         reg_fence_x32(o0);
         reg_fence_x32(o1);
-        if (issuer) tma_store_wait_read();   // the previous store no longer reads the staging buffer
-        ok = group_sync();
-        if (!ok) break;
-        const uint32_t row_addr = stage + row_in_tile * 128;
-        const uint32_t sw = static_cast<uint32_t>(row_in_tile & 7);
+        if (issuer) tma_store_wait_read();   // this warp's previous store no longer reads its staging rows
+        __syncwarp();
+        const uint32_t row_addr = stage + lane * 128;
+        const uint32_t sw = static_cast<uint32_t>(lane & 7);
 #pragma unroll
         for (int c = 0; c < 32; c += 8) {
           st_shared_v4(row_addr + (((c >> 3) ^ sw) << 4),
@@ -486,20 +487,18 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
                        pack2<kBf16>(__uint_as_float(o1[c + 6]) * inv_l, __uint_as_float(o1[c + 7]) * inv_l));
         }
         fence_proxy_async();
-        ok = group_sync();
-        if (!ok) break;
-        if (issuer) {
-          tma_store_4d(&maps.o, stage, c0, tile_row0, h, b);
+        __syncwarp();
+        if (issuer && any_row) {
+          tma_store_4d(&maps.o, stage, c0, tile_row0 + wq * 32, h, b);
           tma_store_commit();
         }
       }
-      if (!ok) break;
       if (p.lse != nullptr && row < S)
         p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);
       tc_fence_before_sync();
       RSFA_TRACE_EV(0x7000);   // epilogue done
     }
-    if (row_in_tile == 0) tma_store_wait_all();   // the last TMA stores must be complete before the CTA exits
+    if (lane == 0) tma_store_wait_all();   // the last TMA stores must be complete before the CTA exits
   }
 
   // ------------------------------------------------------------------ teardown
@@ -521,7 +520,7 @@ cudaError_t launch_db(const FwdParams& p, int sm_count, cudaStream_t stream, lon
   using C = DbCfg<D, NT>;
   TmaMaps maps;
   if (!make_map(&maps.q, p.q, p, p.q_stride, kRowsDb) || !make_map(&maps.k, p.k, p, p.k_stride, kKeysDb) ||
-      !make_map(&maps.v, p.v, p, p.v_stride, kKeysDb) || !make_map(&maps.o, p.o, p, p.o_stride, kRowsDb))
+      !make_map(&maps.v, p.v, p, p.v_stride, kKeysDb) || !make_map(&maps.o, p.o, p, p.o_stride, 32))
     return cudaErrorInvalidValue;
   SchedInfo sched;
   sched.items_per_head = (p.S + NT * kRowsDb - 1) / (NT * kRowsDb);

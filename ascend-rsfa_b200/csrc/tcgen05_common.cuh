@@ -12,14 +12,6 @@ namespace rsfa {
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
-#ifndef RSFA_RESCALE_THRESHOLD
-#define RSFA_RESCALE_THRESHOLD 13.0f
-#endif
-// Lazy rescale: the reference max of a row moves only when the row max grew by more than this many
-// log2 units, so P stays <= 2^13 (fp16 holds 2^16; l and O accumulate in fp32).  With peaked
-// softmax rows (BASELINE cfg2: N(0,1) inputs, sm_scale 0.5) a threshold of 8 still rescaled O in
-// TMEM on most early tiles: 13 is worth +3 % non-causal and +10 % causal there.
-constexpr float kRescaleThreshold = RSFA_RESCALE_THRESHOLD;
 #ifndef RSFA_SUM_LIMIT
 #define RSFA_SUM_LIMIT 32768.0f
 #endif
@@ -116,6 +108,78 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   return r;
 }
 
+
+// Careful version of the softmax of 64 keys (half a 128-key tile, or one 64-key tile), used once a
+// kernel's fast loop has found that a P value might leave the 16-bit range.  It is deliberately
+// NOT inlined and is called only from code behind the fast loop: inside the fast loop even a call
+// to it slowed every step by 5 %.
+// The scores of the half are still intact in tensor memory (P has not been written over them), so
+// they are loaded again: true row maximum, new reference (with headroom) for rows that exceeded
+// the old one, l and (if `rescale`) this thread's row of O_t brought to the new reference, then
+// exp2 / sum / pack and the tcgen05.st of P.  Returns {new reference, l + this half's sum}.
+// `limit` = last visible score of the half (63 if none is masked).  All 32 lanes call it together.
+template <int D, bool kBf16>
+__device__ __noinline__ uint64_t softmax_half_careful(uint32_t t_s, uint32_t t_p, uint32_t t_o, int limit,
+                                                      float scale_log2, float headroom, float m_used, float l,
+                                                      int rescale) {
+  uint32_t a[32], b[32];
+  tmem_ld_x32(t_s, a);
+  tmem_ld_x32(t_s + 32, b);
+  tmem_wait_ld();
+  reg_fence_x32(a);
+  reg_fence_x32(b);
+  if (limit < 63) {
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      if (c > limit) a[c] = 0xff800000u;
+      if (c + 32 > limit) b[c] = 0xff800000u;
+    }
+  }
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int c = 0; c < 32; c += 4) {
+    mx[0] = max3(mx[0], __uint_as_float(a[c]), __uint_as_float(a[c + 1]));
+    mx[1] = max3(mx[1], __uint_as_float(a[c + 2]), __uint_as_float(a[c + 3]));
+    mx[2] = max3(mx[2], __uint_as_float(b[c]), __uint_as_float(b[c + 1]));
+    mx[3] = max3(mx[3], __uint_as_float(b[c + 2]), __uint_as_float(b[c + 3]));
+  }
+  const float mb = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+  float alpha = 1.f;
+  if (mb > m_used) {
+    const float m_new = mb + headroom;
+    alpha = ex2((m_used - m_new) * scale_log2);
+    l *= alpha;
+    m_used = m_new;
+  }
+  if (rescale && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      uint32_t o[32];
+      tmem_ld_x32(t_o + c0, o);
+      tmem_wait_ld();
+      reg_fence_x32(o);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+      tmem_st_x32(t_o + c0, o);
+    }
+  }
+  const float neg_m = -m_used * scale_log2;
+  float h0 = 0.f, h1 = 0.f;
+  uint32_t pk[32];
+#pragma unroll
+  for (int c = 0; c < 32; c += 2) {
+    const float e0 = ex2(fmaf(__uint_as_float(a[c]), scale_log2, neg_m));
+    const float e1 = ex2(fmaf(__uint_as_float(a[c + 1]), scale_log2, neg_m));
+    const float e2 = ex2(fmaf(__uint_as_float(b[c]), scale_log2, neg_m));
+    const float e3 = ex2(fmaf(__uint_as_float(b[c + 1]), scale_log2, neg_m));
+    h0 += e0 + e1;
+    h1 += e2 + e3;
+    pk[c >> 1] = pack2<kBf16>(e0, e1);
+    pk[16 + (c >> 1)] = pack2<kBf16>(e2, e3);
+  }
+  tmem_st_x32(t_p, pk);
+  return pack_f32x2(m_used, l + (h0 + h1));
+}
 
 // Register budgets per warpgroup after the common set-up (launch allocates 168 each):
 // 2 x 128 x 208 + 128 x 80 = 63488 of 65536, so the increase never waits on an exact fit.
