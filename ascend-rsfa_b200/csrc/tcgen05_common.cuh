@@ -183,8 +183,13 @@ __device__ __noinline__ uint64_t softmax_half_careful(uint32_t t_s, uint32_t t_p
 
 // Register budgets per warpgroup after the common set-up (launch allocates 168 each):
 // 2 x 128 x 208 + 128 x 80 = 63488 of 65536, so the increase never waits on an exact fit.
-constexpr int kRegsSoftmax = 208;
-constexpr int kRegsOther = 80;
+#ifndef RSFA_REGS_SOFTMAX
+#define RSFA_REGS_SOFTMAX 208
+#define RSFA_REGS_OTHER 80
+#endif
+constexpr int kRegsSoftmax = RSFA_REGS_SOFTMAX;
+constexpr int kRegsOther = RSFA_REGS_OTHER;
+static_assert(2 * 128 * kRegsSoftmax + 128 * kRegsOther <= 64512, "leave the slack the launch allocation has");
 template <int kRegs>
 __device__ __forceinline__ void setmaxnreg_inc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
