@@ -167,7 +167,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   // setmaxnreg is warpgroup-aligned: every warp of a warpgroup must execute the SAME instruction,
   // so the third warpgroup lowers its budget before it splits into roles.
   if (warp >= kTmaWarp) {
-    setmaxnreg_dec<kRegsOther>();
+    setmaxnreg_dec<RegBudget<D>::kOther>();
   if (warp > kMmaWarp) {
     // idle warps of the third warpgroup
   } else if (warp == kTmaWarp) {
@@ -246,9 +246,6 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       const uint64_t desc_v0 = make_smem_desc_sw128(sKV, C::kKvBoxBytes, 1024);
       uint32_t kv_count = 0, item_count = 0;
       uint32_t p_count[kNT] = {0, 0};
-#ifdef RSFA_EARLY_QK
-      bool early_qk[kNT] = {false, false};   // S_t of the coming item's first key tile is already under way
-#endif
       bool ok = true;
       while (ok) {
         const int slot = item_count & 1;
@@ -304,18 +301,10 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           tc_fence_after_sync();
           RSFA_TRACE_EV(0xa200);   // K_0 present
           for (int t = 0; t < kNT; ++t) {
-#ifdef RSFA_EARLY_QK
-            if (n[t] > 0 && !early_qk[t]) {
-              issue_qk(t, base % C::kStages);
-              umma_commit_elect(bar_s_full(t));
-            }
-            early_qk[t] = false;
-#else
             if (n[t] > 0) {
               issue_qk(t, base % C::kStages);
               umma_commit_elect(bar_s_full(t));
             }
-#endif
             // Q_t is dead once its last QK^T MMA has run: release it so the next item's Q load
             // overlaps the rest of this item.
             if (n[t] <= 1) umma_commit_elect(bar_q_empty(t));
@@ -345,36 +334,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
               RSFA_TRACE_EV(0x3000 + (t << 8) + j);   // P half 1 seen
               issue_pv(t, vidx % C::kStages, true, kTileN / 32, kTileN / 16);
               RSFA_TRACE_EV(0x4000 + (t << 8) + j);   // PV half 1 issued
-              if (j == n[t] - 1) {
-                umma_commit_elect(bar_o_full(t));
-#ifdef RSFA_EARLY_QK
-                // This tile is done with the item.  If the next item is already known and its Q_t
-                // and first K tile have landed, start its first QK^T now instead of after the
-                // other tile's last step and the hand-over between items; the tests do not block.
-                const uint32_t nslot = (item_count + 1) & 1;
-                bool rdy = mbar_test_wait(bar_sched_full0 + 8u * nslot, ((item_count + 1) >> 1) & 1);
-                rdy = __all_sync(0xffffffffu, rdy) != 0;
-                if (rdy) {
-                  const int nitem = __shfl_sync(0xffffffffu, sched_ring[nslot], 0);
-                  if (nitem < sched.total_items) {
-                    int nbh, nrow0;
-                    decode(nitem, nbh, nrow0);
-                    if (num_kv_tiles(nrow0 + t * kTileM, S, p.causal) > 0) {
-                      const uint32_t nbase = base + 2 * nmax;   // ring position of the next item's K_0
-                      bool r2 = mbar_test_wait(bar_q_full(t), (item_count + 1) & 1) &&
-                                mbar_test_wait(bar_kv_full(nbase % C::kStages), (nbase / C::kStages) & 1);
-                      r2 = __all_sync(0xffffffffu, r2) != 0;
-                      if (r2) {
-                        tc_fence_after_sync();
-                        issue_qk(t, nbase % C::kStages);
-                        umma_commit_elect(bar_s_full(t));
-                        early_qk[t] = true;
-                      }
-                    }
-                  }
-                }
-#endif
-              }
+              if (j == n[t] - 1) umma_commit_elect(bar_o_full(t));
             }
             if (j + 1 < n[t]) {
               if (!k_ready) {
@@ -410,7 +370,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   }
   } else {
     // ========================================================== softmax groups
-    setmaxnreg_inc<kRegsSoftmax>();
+    setmaxnreg_inc<RegBudget<D>::kSoftmax>();
     const int t = warp >> 2;                   // Q tile of this group
     const int row_in_tile = (warp & 3) * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;

@@ -58,20 +58,6 @@ enum : int {
   kStatusWaitExpired = 1,  // a bounded wait ran out; low bits say which role
 };
 
-// Non-blocking test of a phase (try_wait may suspend the thread for a while before it gives up).
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
 // try_wait with an explicit suspend-time hint: the hardware may park the thread for up to
 // `hint_ns` nanoseconds (waking it when the phase completes), so a waiting warp does not take
 // issue slots from the warps that are computing on the same scheduler.

@@ -181,15 +181,17 @@ __device__ __noinline__ uint64_t softmax_half_careful(uint32_t t_s, uint32_t t_p
   return pack_f32x2(m_used, l + (h0 + h1));
 }
 
-// Register budgets per warpgroup after the common set-up (launch allocates 168 each):
-// 2 x 128 x 208 + 128 x 80 = 63488 of 65536, so the increase never waits on an exact fit.
-#ifndef RSFA_REGS_SOFTMAX
-#define RSFA_REGS_SOFTMAX 208
-#define RSFA_REGS_OTHER 80
-#endif
-constexpr int kRegsSoftmax = RSFA_REGS_SOFTMAX;
-constexpr int kRegsOther = RSFA_REGS_OTHER;
-static_assert(2 * 128 * kRegsSoftmax + 128 * kRegsOther <= 64512, "leave the slack the launch allocation has");
+// Register budgets per warpgroup after the common set-up (the launch allocates 168 each, 64512 in all):
+// two softmax warpgroups and the warpgroup of the TMA / MMA warps.  The totals stay at or below the
+// launch allocation: a split that needs every register of the file made setmaxnreg.inc wait for ever.
+// D = 128: 200 / 104 (the MMA warp no longer spills; +1 % over 208 / 80); D = 64: 208 / 80 (200 / 104
+// is 6 % slower there).
+template <int D>
+struct RegBudget {
+  static constexpr int kSoftmax = (D == 128) ? 200 : 208;
+  static constexpr int kOther = (D == 128) ? 104 : 80;
+  static_assert(2 * 128 * kSoftmax + 128 * kOther <= 64512, "leave the slack the launch allocation has");
+};
 template <int kRegs>
 __device__ __forceinline__ void setmaxnreg_inc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
