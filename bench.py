@@ -36,8 +36,8 @@ import torch
 
 METRIC = "attention fwd TFLOP/s (whole job; causal FLOPs counted as half)"
 # DRAM bytes (read + write) per (batch, head) of S=2048, D=128 from the ncu capture summarised in
-# profiles/fwd_tcgen05_d128_s2048_ncu_full.md (244.9 MB for 128 heads); traffic is proportional to heads.
-NCU_DRAM_BYTES_PER_HEAD_S2048_D128 = 244.9e6 / 128
+# profiles/fwd_tcgen05_d128_s2048_ncu_full.md (248.9 MB for 128 heads); traffic is proportional to heads.
+NCU_DRAM_BYTES_PER_HEAD_S2048_D128 = 248.9e6 / 128
 FALLBACK_PEAK_TFLOPS = 1590.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 
 
@@ -52,6 +52,9 @@ def parse_args():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the config's batch size (small cases for profiler captures; the default "
+                         "run and every reported number use the config's own)")
     return ap.parse_args()
 
 
@@ -206,6 +209,9 @@ def main():
     torch.cuda.set_device(dev)
 
     B, H, S, D, scale, mult = cfg
+    if args.batch > 0:
+        B = args.batch
+        cfg = (B, H, S, D, scale, mult)
     heads = B * H
     lo, hi = sharding.head_slab(heads, rank, world)
     n_local = hi - lo
