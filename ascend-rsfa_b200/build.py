@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "ascend_rsfa", "librsfa_b200.so")
-SOURCES = ["rsfa_api.cu", "fwd_generic.cu", "fwd_tcgen05.cu", "fwd_tcgen05_db.cu"]
+SOURCES = ["rsfa_api.cu", "fwd_generic.cu", "fwd_tcgen05.cu", "fwd_tcgen05_db.cu", "fwd_tcgen05_sp.cu"]
 HEADERS = ["common.cuh", "ptx_sm100.cuh", "tcgen05_common.cuh", "tile_table.inc", os.path.join("..", "..", "include", "rsfa.h")]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -116,6 +116,8 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint64_t wait_ns = p.wait_limit_ns;
+  // Redo mode with nothing to redo (the usual case): leave before anything is set up.
+  if (sched.redo_count != nullptr && *reinterpret_cast<const volatile int*>(sched.redo_count) == 0) return;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -183,7 +185,9 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         ok = mbar_wait(bar_sched_empty0 + 8u * slot, ((item_count >> 1) & 1) ^ 1, abort_flag, wait_ns,
                        kTagSched);
         if (!ok) break;
-        const int item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
+        int item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
+        if (sched.redo_count != nullptr)
+          item = (item < *sched.redo_count) ? sched.redo_list[item] : sched.total_items;
         sched_ring[slot] = item;
         __threadfence_block();
         mbar_arrive(bar_sched_full0 + 8u * slot);
@@ -193,6 +197,11 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         const int b = bh / p.H, h = bh - b * p.H;
         int nmax = 0;
         for (int t = 0; t < kNT; ++t) nmax = max(nmax, num_kv_tiles(row0 + t * kTileM, S, p.causal));
+#ifdef RSFA_Q_PREFETCH
+        for (int t = 0; t < kNT; ++t)
+          if (row0 + t * kTileM < S)
+            for (int bx = 0; bx < C::kBoxes; ++bx) tma_prefetch_l2_4d(&maps.q, bx * 64, row0 + t * kTileM, h, b);
+#endif
 
         auto load_q = [&](int t) -> bool {
           if (!mbar_wait(bar_q_empty(t), (item_count & 1) ^ 1, abort_flag, wait_ns, kTagQEmpty)) return false;
@@ -218,9 +227,15 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         // K_0 / V_0 first: their ring slots free up while the previous item drains, whereas the
         // Q buffers are released only once that item's last QK^T MMA has finished.
         if (nmax > 0) ok = load_kv(&maps.k, 0);
+#ifdef RSFA_Q_FIRST
+        if (ok) ok = load_q(0);
+        if (ok) ok = load_q(1);
+        if (ok && nmax > 0) ok = load_kv(&maps.v, 0);
+#else
         if (ok && nmax > 0) ok = load_kv(&maps.v, 0);
         if (ok) ok = load_q(0);
         if (ok) ok = load_q(1);
+#endif
         for (int j = 1; ok && j < nmax; ++j) {
           ok = load_kv(&maps.k, j);
           if (ok) ok = load_kv(&maps.v, j);
@@ -639,7 +654,8 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
 }
 
 template <int D, bool kBf16>
-cudaError_t launch_one(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches) {
+cudaError_t launch_one(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches,
+                       bool redo_mode = false) {
   using C = Cfg<D>;
   TmaMaps maps;
   if (!make_map(&maps.q, p.q, p, p.q_stride, kTileM) || !make_map(&maps.k, p.k, p, p.k_stride, kTileN) ||
@@ -648,6 +664,8 @@ cudaError_t launch_one(const FwdParams& p, int sm_count, cudaStream_t stream, lo
   SchedInfo sched;
   sched.items_per_head = (p.S + kNT * kTileM - 1) / (kNT * kTileM);
   sched.total_items = sched.items_per_head * p.B * p.H;
+  sched.redo_list = redo_mode ? p.redo_list : nullptr;
+  sched.redo_count = redo_mode ? p.redo_count : nullptr;
   auto kern = fwd_tcgen05_kernel<D, kBf16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) return e;
@@ -681,8 +699,8 @@ void tcgen05_resolve_tile(int S, int D, int causal, int req_bm, int req_bn, int 
     *bn = 64;
     return;
   }
-  if (variant == 0 || variant == 1) {
-    *bn = variant == 0 ? 128 : 64;
+  if (variant == 0 || variant == 1 || (variant == 2 && D == 64)) {
+    *bn = variant == 1 ? 64 : 128;
     return;
   }
   if (req_bm == 128 && (req_bn == 128 || req_bn == 64)) {  // an instantiated tile: honour the request
@@ -704,8 +722,19 @@ cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t st
   if (p.tile_n == 64 || p.D == 256) return launch_fwd_tcgen05_db(p, sm_count, stream, launches);
   if (p.D == 128) return p.bf16 ? launch_one<128, true>(p, sm_count, stream, launches)
                                 : launch_one<128, false>(p, sm_count, stream, launches);
-  if (p.D == 64) return p.bf16 ? launch_one<64, true>(p, sm_count, stream, launches)
-                               : launch_one<64, false>(p, sm_count, stream, launches);
+  if (p.D == 64) {
+    // D = 64: the separate-P kernel first (it marks the work items whose sum check failed and leaves
+    // their output undefined), then this file's kernel over the marked items only; that second
+    // launch returns at once when there are none.  Without scratch for the marks, or when single-
+    // buffered S is forced, this file's kernel does everything.
+    const bool sp = p.variant != 0 && p.redo_count != nullptr && tcgen05_sp_items(p) <= p.redo_capacity;
+    if (sp) {
+      const cudaError_t e = launch_fwd_tcgen05_sp(p, sm_count, stream, launches);
+      if (e != cudaSuccess) return e;
+    }
+    return p.bf16 ? launch_one<64, true>(p, sm_count, stream, launches, sp)
+                  : launch_one<64, false>(p, sm_count, stream, launches, sp);
+  }
   return cudaErrorInvalidValue;
 }
 
@@ -833,6 +862,11 @@ extern "C" int rsfa_fwd_noalloc(const void* q, const void* k, const void* v, voi
   p.tile_counter = d->scratch;      // cleared by the launcher on `stream` before the kernel
   p.status = reinterpret_cast<int*>(d->scratch + 1);
   p.wait_limit_ns = 2000ull * 1000000ull;
+  p.variant = -1;
+  p.redo_count = nullptr;   // no scratch for the D = 64 separate-P kernel here: the 128-key kernel runs
+  p.redo_flags = nullptr;
+  p.redo_list = nullptr;
+  p.redo_capacity = 0;
 #ifdef RSFA_TRACE
   p.trace = nullptr;
 #endif

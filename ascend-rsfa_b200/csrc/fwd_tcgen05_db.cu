@@ -525,6 +525,8 @@ cudaError_t launch_db(const FwdParams& p, int sm_count, cudaStream_t stream, lon
   SchedInfo sched;
   sched.items_per_head = (p.S + NT * kRowsDb - 1) / (NT * kRowsDb);
   sched.total_items = sched.items_per_head * p.B * p.H;
+  sched.redo_list = nullptr;
+  sched.redo_count = nullptr;
   auto kern = fwd_tcgen05_db_kernel<D, NT, kBf16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) return e;

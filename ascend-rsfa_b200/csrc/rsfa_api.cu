@@ -16,6 +16,12 @@ namespace {
 
 constexpr int kMaxDevices = 64;
 constexpr int kCounterSlots = 1024;  // one work-queue counter per launch in flight
+// Scratch of the D = 64 separate-P kernel: kRedoSlots blocks, used in turn by successive calls, each
+// [counter padded to 4 ints][kRedoCapacity flags][kRedoCapacity item ids].  Larger problems, and the
+// ninth call in flight on one device, are not the target: the former fall back to the 128-key kernel.
+constexpr int kRedoSlots = 8;
+constexpr int kRedoCapacity = 1 << 18;
+constexpr size_t kRedoBlockInts = 4 + 2 * static_cast<size_t>(kRedoCapacity);
 
 struct DeviceState {
   bool ready = false;
@@ -24,6 +30,7 @@ struct DeviceState {
   unsigned int* counters = nullptr;  // kCounterSlots words
   int* status = nullptr;
   unsigned next_slot = 0;
+  int* redo = nullptr;               // kRedoSlots blocks, allocated at the first D = 64 call that can use them
   // staging buffers of rsfa_fwd_host (grow-only)
   void* stage[2][4] = {{nullptr, nullptr, nullptr, nullptr}, {nullptr, nullptr, nullptr, nullptr}};
   float* stage_lse[2] = {nullptr, nullptr};
@@ -142,7 +149,7 @@ int rsfa_set_option(const char* name, long long value) {
   }
 #endif
   if (std::strcmp(name, "tcgen05_variant") == 0) {
-    if (value < -1 || value > 1) return RSFA_ERR_INVALID_ARGUMENT;
+    if (value < -1 || value > 2) return RSFA_ERR_INVALID_ARGUMENT;
     g_tcgen05_variant.store(value);
     return RSFA_OK;
   }
@@ -268,6 +275,11 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
 #ifdef RSFA_TRACE
   p.trace = reinterpret_cast<unsigned long long*>(g_trace_ptr.load());
 #endif
+  p.variant = static_cast<int>(g_tcgen05_variant.load());
+  p.redo_count = nullptr;
+  p.redo_flags = nullptr;
+  p.redo_list = nullptr;
+  p.redo_capacity = 0;
 
   long long launches = 0;
   cudaError_t e;
@@ -276,6 +288,27 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
     int bm = 0, bn = 0;
     tile_of_path(path, S, D, causal, block_m, block_n, &bm, &bn);
     p.tile_n = bn;
+  }
+  if (path == RSFA_PATH_TCGEN05 && D == 64 && p.tile_n == 128 && p.variant != 0 &&
+      rsfa::tcgen05_sp_items(p) <= kRedoCapacity) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (d->redo == nullptr) {
+      int prev = 0;
+      cudaGetDevice(&prev);
+      cudaSetDevice(device);
+      if (cudaMalloc(&d->redo, kRedoSlots * kRedoBlockInts * sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        d->redo = nullptr;   // no scratch: the 128-key kernel does the work
+      }
+      cudaSetDevice(prev);
+    }
+    if (d->redo != nullptr) {
+      int* block = d->redo + (d->next_slot % kRedoSlots) * kRedoBlockInts;
+      p.redo_count = block;
+      p.redo_flags = block + 4;
+      p.redo_list = block + 4 + kRedoCapacity;
+      p.redo_capacity = kRedoCapacity;
+    }
   }
   if (path == RSFA_PATH_TCGEN05)
     e = rsfa::launch_fwd_tcgen05(p, d->sm_count, static_cast<cudaStream_t>(stream), &launches);

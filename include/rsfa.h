@@ -144,8 +144,10 @@ RSFA_API long long rsfa_launch_count(void);
 /*
  * Tuning / test knobs.  Names: "force_path" (-1 auto, 0 generic, 1 tcgen05),
  * "wait_limit_ms" (bound of every in-kernel wait, default 2000), "tcgen05_variant" (-1: the requested tile if
- * instantiated, else the tile table; 0 / 1 force the single-buffered 128-key / double-buffered 64-key
- * kernel for D <= 128), "host_slab_heads"
+ * instantiated, else the tile table, and at D = 64 with 128-key tiles the separate-P kernel followed
+ * by a second launch over the work items it could not finish; 0 / 1 force the single-buffered 128-key /
+ * double-buffered 64-key kernel for D <= 128; 2 forces 128-key tiles with the separate-P kernel where
+ * it exists), "host_slab_heads"
  * (heads per staging slab of rsfa_fwd_host, 0 = automatic).
  * Unknown names -> RSFA_ERR_INVALID_ARGUMENT.
  */

@@ -115,19 +115,33 @@ def test_both_kernel_families_agree(fa, cuda_device, path, causal):
         fa.set_option("force_path", -1)
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("causal", [False, True])
 def test_both_tcgen05_variants(fa, cuda_device, variant, causal):
-    """Single-buffered (128-key tiles) and double-buffered (64-key tiles) kernels of the tcgen05 family."""
+    """Single-buffered (128-key tiles), double-buffered (64-key tiles) and, at D = 64, separate-P kernels."""
     fa.set_option("tcgen05_variant", variant)
-    assert fa.select_path(1024, 128, causal, 0.5)[2] == (128 if variant == 0 else 64)
+    assert fa.select_path(1024, 128, causal, 0.5)[2] == (64 if variant == 1 else 128)
     try:
         for B, H, S, D, scale in [(2, 2, 1024, 128, 0.5), (1, 3, 1536, 64, 0.125), (1, 2, 449, 128, 0.3),
-                                  (1, 2, 191, 64, 0.3), (1, 1, 2048, 128, 2.0)]:
+                                  (1, 2, 191, 64, 0.3), (1, 1, 2048, 128, 2.0), (3, 5, 2304, 64, 0.125),
+                                  (1, 2, 640, 64, 2.0)]:
             q, k, v = make_inputs(B, H, S, D, seed=S + D)
             check(fa, q, k, v, causal, scale, 128, 128, cuda_device)
     finally:
         fa.set_option("tcgen05_variant", -1)
+
+
+def test_separate_p_kernel_marks_items_and_they_are_run_again(fa, cuda_device):
+    # D = 64 with 128-key tiles runs two launches: the separate-P kernel, which cannot redo a key
+    # tile and marks the work items whose sum check failed, and the 128-key kernel over the marked
+    # items.  Near one-hot rows with a growing maximum (sm_scale 3) mark many items; flat rows none.
+    # Both must match the oracle, and the launch counter must show the two launches.
+    q, k, v = make_inputs(2, 3, 1024, 64, seed=31)
+    n0 = fa.launch_count()
+    check(fa, q, k, v, False, 3.0, 128, 128, cuda_device)
+    check(fa, q, k, v, True, 3.0, 128, 128, cuda_device)
+    check(fa, q, k, v, False, 0.125, 128, 128, cuda_device)
+    assert fa.launch_count() - n0 == 6
 
 
 def test_result_does_not_depend_on_requested_tile(fa, cuda_device):
@@ -294,7 +308,7 @@ def test_device_argument_errors(fa, cuda_device):
 
 
 def test_launch_counter_counts_kernels(fa, cuda_device):
-    q = torch.zeros(1, 1, 256, 64, dtype=torch.float16, device=cuda_device)
+    q = torch.zeros(1, 1, 256, 128, dtype=torch.float16, device=cuda_device)
     n0 = fa.launch_count()
     fa.attention(q, q, q, False, 0.5, 128, 128)
     fa.attention(q, q, q, True, 0.5, 128, 128)
