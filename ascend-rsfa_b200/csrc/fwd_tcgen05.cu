@@ -197,11 +197,6 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         const int b = bh / p.H, h = bh - b * p.H;
         int nmax = 0;
         for (int t = 0; t < kNT; ++t) nmax = max(nmax, num_kv_tiles(row0 + t * kTileM, S, p.causal));
-#ifdef RSFA_Q_PREFETCH
-        for (int t = 0; t < kNT; ++t)
-          if (row0 + t * kTileM < S)
-            for (int bx = 0; bx < C::kBoxes; ++bx) tma_prefetch_l2_4d(&maps.q, bx * 64, row0 + t * kTileM, h, b);
-#endif
 
         auto load_q = [&](int t) -> bool {
           if (!mbar_wait(bar_q_empty(t), (item_count & 1) ^ 1, abort_flag, wait_ns, kTagQEmpty)) return false;
@@ -224,18 +219,13 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           ++kv_count;
           return true;
         };
-        // K_0 / V_0 first: their ring slots free up while the previous item drains, whereas the
-        // Q buffers are released only once that item's last QK^T MMA has finished.
+        // K_0 first: its ring slot frees up while the previous item drains.  Then the Q tiles, which
+        // wait for that item's last QK^T, and only then V_0, whose slot frees up last of all: behind
+        // V_0 the Q loads, which come from DRAM, started 2000 clk later than they could.
         if (nmax > 0) ok = load_kv(&maps.k, 0);
-#ifdef RSFA_Q_FIRST
         if (ok) ok = load_q(0);
         if (ok) ok = load_q(1);
         if (ok && nmax > 0) ok = load_kv(&maps.v, 0);
-#else
-        if (ok && nmax > 0) ok = load_kv(&maps.v, 0);
-        if (ok) ok = load_q(0);
-        if (ok) ok = load_q(1);
-#endif
         for (int j = 1; ok && j < nmax; ++j) {
           ok = load_kv(&maps.k, j);
           if (ok) ok = load_kv(&maps.v, j);
@@ -281,25 +271,36 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         }
         // S_t = Q_t K^T : both operands K-major, 64-column boxes, 8-row atoms of 1024 B.  A step
         // of 16 along D moves the start address by 32 B inside the 128-byte swizzle row.
-        auto issue_qk = [&](int t, uint32_t kslot) {
+        // The MMAs of one operand pair and the commits that follow them are issued from ONE elected
+        // region: an elect.sync and a branch per instruction cost the issuing warp more than the
+        // instruction (batched: +3 % at D = 128, +4 % at D = 64).  commit_a / commit_b = 0: none.
+        auto issue_qk = [&](int t, uint32_t kslot, uint32_t commit_a, uint32_t commit_b) {
           const uint64_t qd = desc_q0 + static_cast<uint64_t>((t * C::kQTileBytes) >> 4);
           const uint64_t kd = desc_k0 + static_cast<uint64_t>((kslot * C::kKvTileBytes) >> 4);
+          if (elect_one()) {
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off_q = ((ks >> 2) * C::kQBoxBytes + (ks & 3) * 32) >> 4;
-            const uint32_t off_k = ((ks >> 2) * C::kKvBoxBytes + (ks & 3) * 32) >> 4;
-            umma_ss_elect(tmem_u + C::kColS(t), qd + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
+            for (int ks = 0; ks < D / 16; ++ks) {
+              const uint32_t off_q = ((ks >> 2) * C::kQBoxBytes + (ks & 3) * 32) >> 4;
+              const uint32_t off_k = ((ks >> 2) * C::kKvBoxBytes + (ks & 3) * 32) >> 4;
+              umma_ss(tmem_u + C::kColS(t), qd + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
+            }
+            if (commit_a != 0) umma_commit(commit_a);
+            if (commit_b != 0) umma_commit(commit_b);
           }
+          __syncwarp();
         };
         // O_t (+)= P_t V : A = P_t in TMEM (16 keys = 8 columns per step), B = V MN-major:
         // 16 keys per step = two 8-row atoms (stride 1024 B), 64-column boxes kKvBoxBytes apart.
-        auto issue_pv = [&](int t, uint32_t vslot, bool accumulate, int ks_begin, int ks_end) {
+        auto issue_pv = [&](int t, uint32_t vslot, bool accumulate, int ks_begin, int ks_end, uint32_t commit_a) {
           const uint64_t vd = desc_v0 + static_cast<uint64_t>((vslot * C::kKvTileBytes) >> 4);
+          if (elect_one()) {
 #pragma unroll
-          for (int ks = ks_begin; ks < ks_end; ++ks) {
-            umma_ts_elect(tmem_u + C::kColO(t), tmem_u + C::kColS(t) + ks * 8, vd + ((ks * 2048) >> 4),
-                    idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+            for (int ks = ks_begin; ks < ks_end; ++ks)
+              umma_ts(tmem_u + C::kColO(t), tmem_u + C::kColS(t) + ks * 8, vd + ((ks * 2048) >> 4), idesc_pv,
+                      (accumulate || ks > 0) ? 1u : 0u);
+            if (commit_a != 0) umma_commit(commit_a);
           }
+          __syncwarp();
         };
         auto wait_kv = [&](uint32_t idx) -> bool {
           return wait_all(bar_kv_full(idx % C::kStages), (idx / C::kStages) & 1, kTagKvFull);
@@ -316,13 +317,12 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           tc_fence_after_sync();
           RSFA_TRACE_EV(0xa200);   // K_0 present
           for (int t = 0; t < kNT; ++t) {
-            if (n[t] > 0) {
-              issue_qk(t, base % C::kStages);
-              umma_commit_elect(bar_s_full(t));
-            }
             // Q_t is dead once its last QK^T MMA has run: release it so the next item's Q load
             // overlaps the rest of this item.
-            if (n[t] <= 1) umma_commit_elect(bar_q_empty(t));
+            if (n[t] > 0)
+              issue_qk(t, base % C::kStages, bar_s_full(t), n[t] <= 1 ? bar_q_empty(t) : 0u);
+            else
+              umma_commit_elect(bar_q_empty(t));
           }
           umma_commit_elect(bar_kv_empty(base % C::kStages));
         }
@@ -339,17 +339,15 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
               if (!ok) break;
               tc_fence_after_sync();
               RSFA_TRACE_EV(0x1000 + (t << 8) + j);   // P half 0 seen
-              issue_pv(t, vidx % C::kStages, j > 0, 0, kTileN / 32);
-              umma_commit_elect(bar_pv0_done(t));
+              issue_pv(t, vidx % C::kStages, j > 0, 0, kTileN / 32, bar_pv0_done(t));
               RSFA_TRACE_EV(0x2000 + (t << 8) + j);   // PV half 0 issued
               ok = wait_all(bar_p_full(t, 1), p_count[t] & 1, kTagPFull);
               if (!ok) break;
               ++p_count[t];
               tc_fence_after_sync();
               RSFA_TRACE_EV(0x3000 + (t << 8) + j);   // P half 1 seen
-              issue_pv(t, vidx % C::kStages, true, kTileN / 32, kTileN / 16);
+              issue_pv(t, vidx % C::kStages, true, kTileN / 32, kTileN / 16, j == n[t] - 1 ? bar_o_full(t) : 0u);
               RSFA_TRACE_EV(0x4000 + (t << 8) + j);   // PV half 1 issued
-              if (j == n[t] - 1) umma_commit_elect(bar_o_full(t));
             }
             if (j + 1 < n[t]) {
               if (!k_ready) {
@@ -359,22 +357,16 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
                 k_ready = true;
               }
               RSFA_TRACE_EV(0x9000 + (t << 8) + j);   // K ready
-              issue_qk(t, kidx % C::kStages);
-              RSFA_TRACE_EV(0x5000 + (t << 8) + j);   // QK(j+1) issued
-              umma_commit_elect(bar_s_full(t));
-              RSFA_TRACE_EV(0x8000 + (t << 8) + j);   // S commit issued
-              if (j + 2 == n[t]) umma_commit_elect(bar_q_empty(t));
+              issue_qk(t, kidx % C::kStages, bar_s_full(t), j + 2 == n[t] ? bar_q_empty(t) : 0u);
+              RSFA_TRACE_EV(0x5000 + (t << 8) + j);   // QK(j+1) and its commits issued
             }
           }
           if (!ok) break;
-          umma_commit_elect(bar_kv_empty(vidx % C::kStages));
-          if (j + 1 < nmax) {
-            if (!k_ready) {  // tile loaded for a Q tile that did not need it: still consume it
-              ok = wait_kv(kidx);
-              if (!ok) break;
-            }
-            umma_commit_elect(bar_kv_empty(kidx % C::kStages));
+          if (j + 1 < nmax && !k_ready) {  // tile loaded for a Q tile that did not need it: still consume it
+            ok = wait_kv(kidx);
+            if (!ok) break;
           }
+          umma_commit2_elect(bar_kv_empty(vidx % C::kStages), j + 1 < nmax ? bar_kv_empty(kidx % C::kStages) : 0u);
           RSFA_TRACE_EV(0x7000 + j);   // iteration end
         }
         if (!ok) break;

@@ -225,24 +225,35 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       const int n = num_kv_tiles_db(row0 + t * kRowsDb, S, p.causal);
       // S_t[buf] = Q_t K^T: K-major operands; 16 elements of D per step = 32 B inside a swizzle
       // row, four steps per 64-column box.  `koff` = byte offset of the K tile in the ring.
-      auto issue_qk = [&](int buf, uint32_t koff) {
+      // MMAs and the commits behind them go out from ONE elected region (an elect.sync and a branch
+      // per instruction cost the warp more than the instruction); commit = 0: none.
+      auto issue_qk = [&](int buf, uint32_t koff, uint32_t commit_a, uint32_t commit_b) {
         const uint64_t kd = desc_k0 + static_cast<uint64_t>(koff >> 4);
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off_q = ((ks >> 2) * C::kQBoxBytes + (ks & 3) * 32) >> 4;
-          const uint32_t off_k = ((ks >> 2) * C::kKvBoxBytes + (ks & 3) * 32) >> 4;
-          umma_ss_elect(tmem_u + C::col_s(t, buf), desc_q + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off_q = ((ks >> 2) * C::kQBoxBytes + (ks & 3) * 32) >> 4;
+            const uint32_t off_k = ((ks >> 2) * C::kKvBoxBytes + (ks & 3) * 32) >> 4;
+            umma_ss(tmem_u + C::col_s(t, buf), desc_q + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
+          }
+          if (commit_a != 0) umma_commit(commit_a);
+          if (commit_b != 0) umma_commit(commit_b);
         }
+        __syncwarp();
       };
       // O_t (+)= P V: A = P in TMEM (8 columns per 16 keys), B = V MN-major, N = D spans D/64
       // boxes (kKvBoxBytes apart), 16 keys = two 8-row atoms of 1024 B.
-      auto issue_pv = [&](int buf, uint32_t voff, bool accumulate) {
+      auto issue_pv = [&](int buf, uint32_t voff, bool accumulate, uint32_t commit_a, uint32_t commit_b) {
         const uint64_t vd = desc_v0 + static_cast<uint64_t>(voff >> 4);
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < kKeysDb / 16; ++ks) {
-          umma_ts_elect(col_o, tmem_u + C::col_s(t, buf) + ks * 8, vd + ((ks * 2048) >> 4), idesc_pv,
-                        (accumulate || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < kKeysDb / 16; ++ks)
+            umma_ts(col_o, tmem_u + C::col_s(t, buf) + ks * 8, vd + ((ks * 2048) >> 4), idesc_pv,
+                    (accumulate || ks > 0) ? 1u : 0u);
+          if (commit_a != 0) umma_commit(commit_a);
+          if (commit_b != 0) umma_commit(commit_b);
         }
+        __syncwarp();
       };
 
       ok = wait_all(bar_q_full(t), item_count & 1, kTagQFull);
@@ -254,13 +265,10 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         if (!ok) break;
         tc_fence_after_sync();
         for (int j = 0; j < 2; ++j) {
-          if (j < n) {
-            issue_qk(j, s * C::kSlotBytes + j * C::kKvBytes);
-            umma_commit_elect(bar_s_full(t, j));
-          }
+          if (j < n) issue_qk(j, s * C::kSlotBytes + j * C::kKvBytes, bar_s_full(t, j), 0u);
         }
-        if (n <= 2) umma_commit_elect(bar_q_empty(t));   // Q_t is dead after its last QK^T
-        umma_commit_elect(bar_kv_empty(s));
+        // Q_t is dead after its last QK^T
+        umma_commit2_elect(n <= 2 ? bar_q_empty(t) : 0u, bar_kv_empty(s));
         ++kv_count;
       }
       // entry j + 1: (V_j, K_{j+2})
@@ -276,15 +284,12 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           ++p_count[buf];
           tc_fence_after_sync();
           RSFA_TRACE_EV(0x1000 + j);   // P seen
-          issue_pv(buf, s * C::kSlotBytes, j > 0);
-          umma_commit_elect(bar_pv_done(t));
-          if (j == n - 1) umma_commit_elect(bar_o_full(t));
+          issue_pv(buf, s * C::kSlotBytes, j > 0, bar_pv_done(t), j == n - 1 ? bar_o_full(t) : 0u);
           RSFA_TRACE_EV(0x2000 + j);   // PV issued
         }
         if (j + 2 < n) {
-          issue_qk(buf, s * C::kSlotBytes + C::kKvBytes);   // S_t[buf] is free: PV above consumed P_j in order
-          umma_commit_elect(bar_s_full(t, buf));
-          if (j + 3 == n) umma_commit_elect(bar_q_empty(t));
+          // S_t[buf] is free: PV above consumed P_j in order
+          issue_qk(buf, s * C::kSlotBytes + C::kKvBytes, bar_s_full(t, buf), j + 3 == n ? bar_q_empty(t) : 0u);
           RSFA_TRACE_EV(0x5000 + j);   // QK(j+2) issued
         }
         umma_commit_elect(bar_kv_empty(s));

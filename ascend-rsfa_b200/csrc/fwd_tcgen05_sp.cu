@@ -221,21 +221,32 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         const int n = num_kv_tiles_sp(row0 + t * kRows, S, p.causal);
         // S_t = Q_t K^T: both operands K-major in one 64-column box; 16 elements of D per step
         // = 32 B inside the 128-byte swizzle row.
-        auto issue_qk = [&](uint32_t kslot) {
+        // MMAs and the commits behind them go out from ONE elected region (an elect.sync and a
+        // branch per instruction cost the warp more than the instruction); commit = 0: none.
+        auto issue_qk = [&](uint32_t kslot, uint32_t commit_a, uint32_t commit_b) {
           const uint64_t kd = desc_k0 + static_cast<uint64_t>((kslot * kKvBytes) >> 4);
+          if (elect_one()) {
 #pragma unroll
-          for (int ks = 0; ks < kD / 16; ++ks)
-            umma_ss_elect(tmem_u + kColS(t), desc_q + ((ks * 32) >> 4), kd + ((ks * 32) >> 4), idesc_qk,
-                          ks > 0 ? 1u : 0u);
+            for (int ks = 0; ks < kD / 16; ++ks)
+              umma_ss(tmem_u + kColS(t), desc_q + ((ks * 32) >> 4), kd + ((ks * 32) >> 4), idesc_qk, ks > 0 ? 1u : 0u);
+            if (commit_a != 0) umma_commit(commit_a);
+            if (commit_b != 0) umma_commit(commit_b);
+          }
+          __syncwarp();
         };
         // O_t (+)= P_t V: A = P_t in TMEM (16 keys = 8 columns per step), B = V MN-major:
         // 16 keys per step = two 8-row atoms of 1024 B.
-        auto issue_pv = [&](uint32_t vslot, bool accumulate) {
+        auto issue_pv = [&](uint32_t vslot, bool accumulate, uint32_t commit_a, uint32_t commit_b) {
           const uint64_t vd = desc_v0 + static_cast<uint64_t>((vslot * kKvBytes) >> 4);
+          if (elect_one()) {
 #pragma unroll
-          for (int ks = 0; ks < kKeys / 16; ++ks)
-            umma_ts_elect(tmem_u + kColO(t), tmem_u + kColP(t) + ks * 8, vd + ((ks * 2048) >> 4), idesc_pv,
-                          (accumulate || ks > 0) ? 1u : 0u);
+            for (int ks = 0; ks < kKeys / 16; ++ks)
+              umma_ts(tmem_u + kColO(t), tmem_u + kColP(t) + ks * 8, vd + ((ks * 2048) >> 4), idesc_pv,
+                      (accumulate || ks > 0) ? 1u : 0u);
+            if (commit_a != 0) umma_commit(commit_a);
+            if (commit_b != 0) umma_commit(commit_b);
+          }
+          __syncwarp();
         };
         auto wait_kv = [&](uint32_t idx) -> bool {
           return wait_all(bar_kv_full(idx % kStagesSp), (idx / kStagesSp) & 1, kTagKvFull);
@@ -249,11 +260,10 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           if (!ok) break;
           tc_fence_after_sync();
           // S_t is free: the previous item's last P was produced after its S had been read.
-          if (n > 0) {
-            issue_qk(base % kStagesSp);
-            umma_commit_elect(bar_s_full(t));
-          }
-          if (n <= 1) umma_commit_elect(bar_q_empty(t));
+          if (n > 0)
+            issue_qk(base % kStagesSp, bar_s_full(t), n <= 1 ? bar_q_empty(t) : 0u);
+          else
+            umma_commit_elect(bar_q_empty(t));
           umma_commit_elect(bar_kv_empty(base % kStagesSp));
         }
         for (int j = 0; ok && j < nmax; ++j) {
@@ -267,9 +277,7 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
               ok = wait_all(bar_s_free(t), (sf_count + j) & 1, kTagSFull);
               if (!ok) break;
               tc_fence_after_sync();
-              issue_qk(kidx % kStagesSp);
-              umma_commit_elect(bar_s_full(t));
-              if (j + 2 == n) umma_commit_elect(bar_q_empty(t));
+              issue_qk(kidx % kStagesSp, bar_s_full(t), j + 2 == n ? bar_q_empty(t) : 0u);
             }
             umma_commit_elect(bar_kv_empty(kidx % kStagesSp));
           }
@@ -279,9 +287,7 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
             ok = wait_all(bar_p_full(t), (p_count + j) & 1, kTagPFull);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_pv(vidx % kStagesSp, j > 0);
-            umma_commit_elect(bar_p_free(t));
-            if (j == n - 1) umma_commit_elect(bar_o_full(t));
+            issue_pv(vidx % kStagesSp, j > 0, bar_p_free(t), j == n - 1 ? bar_o_full(t) : 0u);
           }
           umma_commit_elect(bar_kv_empty(vidx % kStagesSp));
         }
@@ -394,18 +400,7 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
             float x0, x1, x2, x3;
             unpack_f32x2(xa, x0, x1);
             unpack_f32x2(xb, x2, x3);
-            const float e0 = ex2(x0), e1 = ex2(x1);
-            float e2, e3;
-#ifndef RSFA_SP_POLY_MASK
-#define RSFA_SP_POLY_MASK -1
-#endif
-            // every RSFA_SP_POLY_MASK-selected pair goes to the FMA pipe (mask 4: a quarter of all)
-            if (RSFA_SP_POLY_MASK >= 0 && (c & RSFA_SP_POLY_MASK) == 0) {
-              exp2_poly_x2(xb, e2, e3);
-            } else {
-              e2 = ex2(x2);
-              e3 = ex2(x3);
-            }
+            const float e0 = ex2(x0), e1 = ex2(x1), e2 = ex2(x2), e3 = ex2(x3);
             sum_a = add_f32x2(sum_a, pack_f32x2(e0, e1));
             sum_b = add_f32x2(sum_b, pack_f32x2(e2, e3));
             pk[base + (c >> 1)] = pack2<kBf16>(e0, e1);

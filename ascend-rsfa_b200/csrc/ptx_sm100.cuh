@@ -132,13 +132,6 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap
       : "memory");
 }
 
-// Bring one tiled 4-D box into L2 ahead of its load (no shared-memory destination, no completion).
-__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
-  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(map), "r"(c0),
-               "r"(c1), "r"(c2), "r"(c3)
-               : "memory");
-}
-
 // One tiled 4-D box, this CTA's shared memory -> global (rows outside the tensor are clipped).
 // Completion is tracked per thread in bulk groups.
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t smem_src, int c0, int c1, int c2,
@@ -238,6 +231,15 @@ __device__ __forceinline__ void umma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, 
 }
 __device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
   if (elect_one()) umma_commit(bar);
+}
+// Two commits from one elected region (0 = no barrier): an elect.sync and a branch per instruction
+// cost the issuing warp more than the instruction itself.
+__device__ __forceinline__ void umma_commit2_elect(uint32_t bar_a, uint32_t bar_b) {
+  if (elect_one()) {
+    if (bar_a != 0) umma_commit(bar_a);
+    if (bar_b != 0) umma_commit(bar_b);
+  }
+  __syncwarp();
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle (the layout TMA writes with

@@ -185,34 +185,6 @@ __device__ __noinline__ uint64_t softmax_half_careful(uint32_t t_s, uint32_t t_p
   return pack_f32x2(m_used, l + (h0 + h1));
 }
 
-// exp2 of two lanes on the FMA pipe instead of the MUFU: round-to-nearest split x = n + r with
-// |r| <= 0.5 (adding 1.5 * 2^23 leaves n in the low mantissa bits), a cubic for 2^r (maximum
-// relative error 7.6e-5, well below half an ulp of the 16-bit P it is rounded to), and n added
-// into the exponent field.  Inputs are clamped at -126 so the exponent arithmetic cannot wrap
-// (masked scores are -inf).  Worth it only where the softmax warps are MUFU-bound (two warps per
-// scheduler running back to back: the D = 64 separate-P kernel); the 128-key kernels lost with it.
-__device__ __forceinline__ void exp2_poly_x2(uint64_t x2v, float& e0, float& e1) {
-  float x0, x1;
-  unpack_f32x2(x2v, x0, x1);
-  x0 = fmaxf(x0, -126.f);
-  x1 = fmaxf(x1, -126.f);
-  const uint64_t xc = pack_f32x2(x0, x1);
-  const uint64_t magic = pack_f32x2(12582912.f, 12582912.f);
-  const uint64_t neg_magic = pack_f32x2(-12582912.f, -12582912.f);
-  const uint64_t minus1 = pack_f32x2(-1.f, -1.f);
-  const uint64_t t = add_f32x2(xc, magic);
-  const uint64_t n = add_f32x2(t, neg_magic);
-  const uint64_t r = fma_f32x2(n, minus1, xc);
-  uint64_t q = fma_f32x2(pack_f32x2(0.055205513f, 0.055205513f), r, pack_f32x2(0.24261397f, 0.24261397f));
-  q = fma_f32x2(q, r, pack_f32x2(0.69325477f, 0.69325477f));
-  q = fma_f32x2(q, r, pack_f32x2(0.9999277f, 0.9999277f));
-  float t0, t1, q0, q1;
-  unpack_f32x2(t, t0, t1);
-  unpack_f32x2(q, q0, q1);
-  e0 = __uint_as_float((__float_as_uint(t0) << 23) + __float_as_uint(q0));
-  e1 = __uint_as_float((__float_as_uint(t1) << 23) + __float_as_uint(q1));
-}
-
 // Register budgets per warpgroup after the common set-up (the launch allocates 168 each, 64512 in all):
 // two softmax warpgroups and the warpgroup of the TMA / MMA warps.  The totals stay at or below the
 // launch allocation: a split that needs every register of the file made setmaxnreg.inc wait for ever.
