@@ -36,8 +36,8 @@ import torch
 
 METRIC = "attention fwd TFLOP/s (whole job; causal FLOPs counted as half)"
 # DRAM bytes (read + write) per (batch, head) of S=2048, D=128 from the ncu capture summarised in
-# profiles/fwd_tcgen05_d128_s2048_ncu_full.md (248.9 MB for 128 heads); traffic is proportional to heads.
-NCU_DRAM_BYTES_PER_HEAD_S2048_D128 = 248.9e6 / 128
+# profiles/fwd_tcgen05_d128_s2048_ncu_full.md (249.4 MB for 128 heads); traffic is proportional to heads.
+NCU_DRAM_BYTES_PER_HEAD_S2048_D128 = 249.4e6 / 128
 FALLBACK_PEAK_TFLOPS = 1590.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 
 
