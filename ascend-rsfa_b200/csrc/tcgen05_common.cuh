@@ -185,16 +185,19 @@ __device__ __noinline__ uint64_t softmax_half_careful(uint32_t t_s, uint32_t t_p
   return pack_f32x2(m_used, l + (h0 + h1));
 }
 
-// Register budgets per warpgroup after the common set-up (the launch allocates 168 each, 64512 in all):
-// two softmax warpgroups and the warpgroup of the TMA / MMA warps.  The totals stay at or below the
-// launch allocation: a split that needs every register of the file made setmaxnreg.inc wait for ever.
-// D = 128: 200 / 104 (the MMA warp no longer spills; +1 % over 208 / 80); D = 64: 208 / 80 (200 / 104
-// is 6 % slower there).
+// Register budgets per warpgroup after the common set-up of the 384-thread kernels (the launch
+// allocates 168 per thread): two softmax warpgroups and the warpgroup of the TMA / MMA warps.
+// setmaxnreg.inc can only take registers that another warpgroup of the same CTA has released with
+// setmaxnreg.dec: an increase that asks for more than was released waits for ever (it did, with
+// 208 / 96).  D = 128: 200 / 104 (the MMA warp no longer spills; +1 % over 208 / 80); D = 64:
+// 208 / 80 (200 / 104 is 6 % slower there).
 template <int D>
 struct RegBudget {
+  static constexpr int kLaunch = 168;
   static constexpr int kSoftmax = (D == 128) ? 200 : 208;
   static constexpr int kOther = (D == 128) ? 104 : 80;
-  static_assert(2 * 128 * kSoftmax + 128 * kOther <= 64512, "leave the slack the launch allocation has");
+  static_assert(128 * (kLaunch - kOther) >= 2 * 128 * (kSoftmax - kLaunch),
+                "the softmax warpgroups can only take what the third warpgroup releases");
 };
 template <int kRegs>
 __device__ __forceinline__ void setmaxnreg_inc() {
