@@ -48,6 +48,8 @@ def get_num_compute_cores():
 def _dense(t):
     """The C ABI wants a unit innermost stride, the other strides multiples of 8 elements and a
     16-byte aligned base; anything else is copied once."""
+    if t.is_contiguous() and t.shape[-1] % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t                      # the usual case, decided without walking the strides
     ok = t.stride(-1) == 1 and t.data_ptr() % 16 == 0
     if ok:
         D = t.shape[-1]
@@ -75,13 +77,17 @@ def _forward(q, k, v, causal, sm_scale, BM, BN, want_lse):
         o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     M = torch.empty((Z, H, N_CTX), dtype=torch.float32, device=q.device) if want_lse else None
     strides = (ctypes.c_int64 * 16)(*qd.stride(), *kd.stride(), *vd.stride(), *o.stride())
-    with torch.cuda.device(q.device):
-        stream = torch.cuda.current_stream().cuda_stream
-        rc = _lib.rsfa_fwd(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(),
-                           M.data_ptr() if M is not None else None,
-                           Z, H, N_CTX, HEAD_DIM, strides, 1 if causal else 0, float(sm_scale),
-                           int(BM), int(BN), _DTYPES[q.dtype], stream)
-    _capi.check(rc, "rsfa_fwd")
+    args = (qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), M.data_ptr() if M is not None else None,
+            Z, H, N_CTX, HEAD_DIM, strides, 1 if causal else 0, float(sm_scale), int(BM), int(BN),
+            _DTYPES[q.dtype])
+    # rsfa_fwd launches on the CURRENT device; switching costs microseconds, so only when needed
+    if q.device.index == torch.cuda.current_device():
+        rc = _lib.rsfa_fwd(*args, torch.cuda.current_stream().cuda_stream)
+    else:
+        with torch.cuda.device(q.device):
+            rc = _lib.rsfa_fwd(*args, torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        _capi.check(rc, "rsfa_fwd")
     return o, M
 
 
@@ -92,8 +98,10 @@ class _attention(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, causal, sm_scale, BM, BN):
-        o, M = _forward(q, k, v, causal, sm_scale, BM, BN, want_lse=True)
-        ctx.save_for_backward(q, k, v, o, M)
+        # The reference keeps the log-sum-exp for a backward pass it does not have (:400-404, :616);
+        # with no backward here either it is not computed on this path: attention_with_lse() returns it.
+        o, _ = _forward(q, k, v, causal, sm_scale, BM, BN, want_lse=False)
+        ctx.save_for_backward(q, k, v, o)
         ctx.sm_scale = sm_scale
         ctx.HEAD_DIM = q.shape[-1]
         ctx.causal = causal

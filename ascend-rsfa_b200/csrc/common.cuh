@@ -1,5 +1,6 @@
 // Types shared by the kernels and the C-ABI dispatcher.
 #pragma once
+#include <atomic>
 #include <cstdint>
 #include <cuda_runtime.h>
 
@@ -36,6 +37,19 @@ struct FwdParams {
   unsigned long long* trace;  // debug builds only: per-role event log of CTA 0
 #endif
 };
+
+// Raises a kernel's dynamic shared-memory limit once per device instead of on every call (the
+// attribute stays with the function in that device's context).  `done` is a bit mask by device
+// ordinal, one per kernel instantiation (a static of the launcher that owns the kernel).
+inline cudaError_t set_dynamic_smem_once(std::atomic<unsigned long long>& done, const void* kern, int bytes) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 64 && ((done.load(std::memory_order_acquire) >> dev) & 1ull)) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
+  return e;
+}
 
 // Launchers implemented in the kernel translation units.  Each returns a cudaError_t
 // from the launch itself and bumps *launches by the number of kernels it started.

@@ -247,7 +247,8 @@ template <int D, bool kBf16>
 cudaError_t launch_one(const FwdParams& p, cudaStream_t stream) {
   using Cfg = GenericCfg<D>;
   auto kern = fwd_generic_kernel<D, kBf16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  static std::atomic<unsigned long long> smem_done{0};   // per kernel instantiation, bit per device
+  cudaError_t e = set_dynamic_smem_once(smem_done, reinterpret_cast<const void*>(kern), Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((p.S + kBM - 1) / kBM, p.B * p.H);
   kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(p);

@@ -659,7 +659,8 @@ cudaError_t launch_one(const FwdParams& p, int sm_count, cudaStream_t stream, lo
   sched.redo_list = redo_mode ? p.redo_list : nullptr;
   sched.redo_count = redo_mode ? p.redo_count : nullptr;
   auto kern = fwd_tcgen05_kernel<D, kBf16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  static std::atomic<unsigned long long> smem_done{0};   // per kernel instantiation, bit per device
+  cudaError_t e = set_dynamic_smem_once(smem_done, reinterpret_cast<const void*>(kern), C::kSmemBytes);
   if (e != cudaSuccess) return e;
   e = cudaMemsetAsync(p.tile_counter, 0, sizeof(unsigned int), stream);
   if (e != cudaSuccess) return e;
@@ -719,7 +720,9 @@ cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t st
     // their output undefined), then this file's kernel over the marked items only; that second
     // launch returns at once when there are none.  Without scratch for the marks, or when single-
     // buffered S is forced, this file's kernel does everything.
-    const bool sp = p.variant != 0 && p.redo_count != nullptr && tcgen05_sp_items(p) <= p.redo_capacity;
+    // A single key tile (S <= 128) leaves nothing to overlap: one launch of this file's kernel then.
+    const bool sp = p.variant != 0 && p.redo_count != nullptr && tcgen05_sp_items(p) <= p.redo_capacity &&
+                    (p.S > kTileN || p.variant == 2);
     if (sp) {
       const cudaError_t e = launch_fwd_tcgen05_sp(p, sm_count, stream, launches);
       if (e != cudaSuccess) return e;

@@ -533,7 +533,8 @@ cudaError_t launch_db(const FwdParams& p, int sm_count, cudaStream_t stream, lon
   sched.redo_list = nullptr;
   sched.redo_count = nullptr;
   auto kern = fwd_tcgen05_db_kernel<D, NT, kBf16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  static std::atomic<unsigned long long> smem_done{0};   // per kernel instantiation, bit per device
+  cudaError_t e = set_dynamic_smem_once(smem_done, reinterpret_cast<const void*>(kern), C::kSmemBytes);
   if (e != cudaSuccess) return e;
   e = cudaMemsetAsync(p.tile_counter, 0, sizeof(unsigned int), stream);
   if (e != cudaSuccess) return e;

@@ -518,7 +518,8 @@ static cudaError_t launch_sp_one(const FwdParams& p, int sm_count, cudaStream_t 
   if (p.redo_count == nullptr || p.redo_flags != p.redo_count + 4 || sched.total_items > p.redo_capacity)
     return cudaErrorInvalidValue;
   auto kern = fwd_tcgen05_sp_kernel<kBf16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesSp);
+  static std::atomic<unsigned long long> smem_done{0};   // per kernel instantiation, bit per device
+  cudaError_t e = set_dynamic_smem_once(smem_done, reinterpret_cast<const void*>(kern), kSmemBytesSp);
   if (e != cudaSuccess) return e;
   e = cudaMemsetAsync(p.tile_counter, 0, sizeof(unsigned int), stream);
   if (e != cudaSuccess) return e;

@@ -83,15 +83,22 @@ int ensure_device(int device, DeviceState** out) {
 
 bool valid_head_dim(int D) { return D == 16 || D == 32 || D == 64 || D == 128 || D == 256; }
 
-// Kernel family by shape: sequences of at most 128 keys are a single tile and go to the
-// short-sequence kernel, like the reference's N_CTX <= 128 rule (:564); longer ones go to the
-// tcgen05 kernel where it is instantiated.
-int choose_path(int S, int D, float sm_scale) {
+// Kernel family by shape.  Sequences of at most 128 keys are a single tile: small batches of them
+// go to the short-sequence kernel, like the reference's N_CTX <= 128 rule (:564) - it starts faster
+// (26 against 28 to 33 us per call at a handful of heads).  From kShortSeqHeads heads on, the
+// tcgen05 kernel takes them too where it is instantiated: it runs such batches at the HBM rate
+// (512 x 8 heads of S = 128, D = 128: 87 us = 6.2 TB/s against 304 us), the mma.sync kernel does
+// not; only S <= 64 at D = 64 stays (72 against 85 us).  Longer sequences go to the tcgen05 kernel
+// where it is instantiated.
+constexpr long long kShortSeqHeads = 256;
+int choose_path(int S, int D, float sm_scale, long long heads) {
   const long long forced = g_force_path.load();
   const bool tc_ok = rsfa::tcgen05_supports(S, D, sm_scale);
   if (forced == RSFA_PATH_GENERIC) return RSFA_PATH_GENERIC;
   if (forced == RSFA_PATH_TCGEN05 && tc_ok) return RSFA_PATH_TCGEN05;
-  return (tc_ok && S > 128) ? RSFA_PATH_TCGEN05 : RSFA_PATH_GENERIC;
+  if (!tc_ok) return RSFA_PATH_GENERIC;
+  if (S > 128) return RSFA_PATH_TCGEN05;
+  return (heads >= kShortSeqHeads && !(S <= 64 && D == 64)) ? RSFA_PATH_TCGEN05 : RSFA_PATH_GENERIC;
 }
 
 // Tile a call runs: on the tcgen05 path the request is honoured when instantiated, otherwise the
@@ -182,7 +189,7 @@ int rsfa_select_path(int S, int D, int causal, float sm_scale, int block_m, int 
   if (path == nullptr || S < 1 || !valid_head_dim(D) || block_m < 1 || block_n < 1 ||
       (dtype != RSFA_DTYPE_F16 && dtype != RSFA_DTYPE_BF16))
     return RSFA_ERR_INVALID_ARGUMENT;
-  *path = choose_path(S, D, sm_scale);
+  *path = choose_path(S, D, sm_scale, 1);   // no batch here: the answer for a small batch
   int bm, bn;
   tile_of_path(*path, S, D, causal, block_m, block_n, &bm, &bn);
   if (tile_m != nullptr) *tile_m = bm;
@@ -283,7 +290,7 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
 
   long long launches = 0;
   cudaError_t e;
-  const int path = choose_path(S, D, sm_scale);
+  const int path = choose_path(S, D, sm_scale, static_cast<long long>(B) * H);
   {
     int bm = 0, bn = 0;
     tile_of_path(path, S, D, causal, block_m, block_n, &bm, &bn);

@@ -131,6 +131,19 @@ def test_both_tcgen05_variants(fa, cuda_device, variant, causal):
         fa.set_option("tcgen05_variant", -1)
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_large_batches_of_short_sequences_take_the_tcgen05_kernel(fa, cuda_device, causal):
+    # From 256 heads on, sequences of at most 128 keys run on the tcgen05 kernel (HBM-bound there);
+    # one work item is then a single, partly empty pair of Q tiles.  The launch counter shows
+    # one launch either way (a single key tile does not use the D = 64 two-launch scheme).
+    for B, H, S, D, scale in [(40, 8, 128, 128, 0.3), (33, 8, 96, 64, 0.25), (32, 8, 128, 256, 0.0625),
+                              (64, 4, 77, 128, 0.3), (64, 4, 64, 64, 0.25), (2, 4, 128, 128, 0.3)]:
+        q, k, v = make_inputs(B, H, S, D, seed=S + D + B)
+        n0 = fa.launch_count()
+        check(fa, q, k, v, causal, scale, 128, 128, cuda_device)
+        assert fa.launch_count() - n0 == 1, (B, H, S, D)
+
+
 def test_separate_p_kernel_marks_items_and_they_are_run_again(fa, cuda_device):
     # D = 64 with 128-key tiles runs two launches: the separate-P kernel, which cannot redo a key
     # tile and marks the work items whose sum check failed, and the 128-key kernel over the marked
