@@ -89,6 +89,19 @@ def test_options_round_trip():
         fa.set_option("no_such_option", 1)
     with pytest.raises(ValueError):
         fa.set_option("force_path", 5)
+    # -1 automatic, 0 single-buffered 128-key kernel, 1 double-buffered 64-key kernel, 2 separate-P kernel
+    for variant in (0, 1, 2, -1):
+        fa.set_option("tcgen05_variant", variant)
+        assert lib.rsfa_get_option(b"tcgen05_variant") == variant
+    with pytest.raises(ValueError):
+        fa.set_option("tcgen05_variant", 3)
+    # forcing a variant decides the tile the family runs (2 exists at D = 64 only)
+    fa.set_option("tcgen05_variant", 1)
+    assert fa.select_path(4096, 64, False, 0.125) == (1, 128, 64)
+    fa.set_option("tcgen05_variant", 2)
+    assert fa.select_path(512, 64, True, 0.125, 128, 64) == (1, 128, 128)
+    assert fa.select_path(512, 128, True, 0.125, 128, 64) == (1, 128, 64)
+    fa.set_option("tcgen05_variant", -1)
 
 
 @pytest.mark.parametrize("heads,world", [(1024, 8), (512, 4), (128, 8), (2, 2), (7, 4), (3, 8)])
