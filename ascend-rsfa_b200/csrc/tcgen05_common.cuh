@@ -21,7 +21,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 // The reference maximum of a row is placed this many log2 units ABOVE the largest score seen when
 // it is set, so P starts at <= 2^-6 and a row can grow by 21 log2 units before anything has to be
 // rescaled.  fp16 keeps full precision down to 2^-14, i.e. for weights down to 2^-8 of the row's
-// largest, and denormals (absolute error 2^-19 of the largest weight) below that.  On BASELINE
+// largest, and denormals (absolute error 2^-19 of the largest weight) below that.  On benchmark configuration
 // cfg2 (N(0,1) inputs, sm_scale 0.5: near one-hot rows) 0.6 % of the warp-steps still took the
 // careful path with a headroom of 4; 4 -> 6 -> 8 gave 1171 -> 1194 -> 1206 TFLOP/s there.
 constexpr float kHeadroomLog2 = RSFA_HEADROOM;

@@ -59,7 +59,7 @@ def main():
     g = torch.Generator(device=dev).manual_seed(42)
     best = {}
     for S, D, heads in SWEEP:
-        # two logit distributions: the usual 1/sqrt(D) and the peaked rows of the BASELINE cfg2
+        # two logit distributions: the usual 1/sqrt(D) and the peaked rows of benchmark configuration cfg2 (sm_scale 0.5)
         # recipe (sm_scale 0.5 on N(0,1) inputs), where O is rescaled much more often
         scales = (1.0 / D ** 0.5, 0.5)
         q, k, v = [torch.randn(1, heads, S, D, generator=g, device=dev).half() for _ in range(3)]

@@ -5,7 +5,7 @@
                     [--config cfg2] [--causal 0|1] [--e2e-steps E]
 
 One "step" is one forward pass of `attention()` over the whole configured batch
-(default: BASELINE cfg2 — B=128, H=8, S=2048, D=128, fp16, sm_scale=0.5,
+(default: benchmark configuration cfg2 — B=128, H=8, S=2048, D=128, fp16, sm_scale=0.5,
 non-causal; the causal pass of the same shape is timed separately and reported
 under "causal").  For N > 1 the script is launched with torchrun, one rank per
 GPU; the B*H heads of the SAME problem are split across ranks (no collective in

@@ -131,7 +131,7 @@ def error_metrics(out, ref, atol=1e-2, rtol=1e-2):
     }
 
 
-# BASELINE configurations: (B, H, S, D, sm_scale, input multiplier).
+# Benchmark configurations: (B, H, S, D, sm_scale, input multiplier).
 CONFIGS = {
     "cfg1": (1, 2, 128, 64, 0.5, 1.0),
     "cfg2": (128, 8, 2048, 128, 0.5, 1.0),

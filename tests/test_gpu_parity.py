@@ -251,7 +251,7 @@ def test_requires_grad_inputs_and_no_backward(fa, cuda_device):
 
 
 def test_size_independent_properties_at_full_cfg2_heads(fa, cuda_device):
-    """At BASELINE cfg2's per-head size (S=2048, D=128) on many heads: rows of P sum to one
+    """At benchmark configuration cfg2's per-head size (S=2048, D=128) on many heads: rows of P sum to one
     (V = ones -> O = ones), causal row 0 equals v[0], and a uniform shift of the logits
     (adding a constant vector to every key along q) leaves the output unchanged."""
     B, H, S, D = 4, 8, 2048, 128

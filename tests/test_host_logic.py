@@ -9,12 +9,12 @@ from ascend_rsfa import _capi, sharding
 
 lib = _capi.load()
 
-BASELINE_SHAPES = [
+CONFIG_SHAPES = [
     (1, 2, 128, 64), (128, 8, 2048, 128), (64, 8, 1024, 256), (16, 16, 4096, 128), (4, 32, 8192, 64),
 ]
 
 
-@pytest.mark.parametrize("shape", BASELINE_SHAPES)
+@pytest.mark.parametrize("shape", CONFIG_SHAPES)
 @pytest.mark.parametrize("causal", [False, True])
 def test_get_tiling_covers_every_baseline_config(shape, causal):
     bm, bn = fa.get_tiling(*shape, causal)
