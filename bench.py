@@ -35,8 +35,9 @@ sys.path.insert(0, os.path.join(ROOT, "ascend-rsfa_b200"))
 import torch
 
 METRIC = "attention fwd TFLOP/s (whole job; causal FLOPs counted as half)"
-# DRAM bytes (read + write) per (batch, head) of S=2048, D=128 from the ncu capture summarised in
-# profiles/fwd_tcgen05_d128_s2048_ncu_full.md (249.4 MB for 128 heads); traffic is proportional to heads.
+# DRAM bytes (read + write) per (batch, head) of S=2048, D=128: dram__bytes_read.sum + dram__bytes_write.sum
+# of one ncu capture of this kernel on 128 heads of the shape (201.4 + 48.0 MB); traffic is proportional
+# to the number of heads (Q, K, V read once, O written once; the re-reads of K/V are served by L2).
 NCU_DRAM_BYTES_PER_HEAD_S2048_D128 = 249.4e6 / 128
 FALLBACK_PEAK_TFLOPS = 1590.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 
