@@ -444,40 +444,11 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       tc_fence_after_sync();
       const float inv_l = 1.f / l;
       const int b = bh / p.H, h = bh - b * p.H;
-      // Each warp stages its 32 rows (128-byte swizzle) and stores them with one TMA store; rows
-      // past S are clipped, a warp whose rows all lie past S stores nothing.
-      const int wq = warp & 3;
-      const uint32_t stage = sStage + t * kStageBytesSp + wq * 4096;
+      // O_t / l -> global memory: each warp stages and stores its own 32 rows (store_o_rows)
       {
-        uint32_t o0[32], o1[32];
-        tmem_ld_x32(tO, o0);
-        tmem_ld_x32(tO + 32, o1);
-        tmem_wait_ld();
-        reg_fence_x32(o0);
-        reg_fence_x32(o1);
-        if (lane == 0) tma_store_wait_read();   // this warp's previous store no longer reads its staging rows
-        __syncwarp();
-        const uint32_t row_addr = stage + lane * 128;
-        const uint32_t sw = static_cast<uint32_t>(lane & 7);
-#pragma unroll
-        for (int c = 0; c < 32; c += 8) {
-          st_shared_v4(row_addr + (((c >> 3) ^ sw) << 4),
-                       pack2<kBf16>(__uint_as_float(o0[c + 0]) * inv_l, __uint_as_float(o0[c + 1]) * inv_l),
-                       pack2<kBf16>(__uint_as_float(o0[c + 2]) * inv_l, __uint_as_float(o0[c + 3]) * inv_l),
-                       pack2<kBf16>(__uint_as_float(o0[c + 4]) * inv_l, __uint_as_float(o0[c + 5]) * inv_l),
-                       pack2<kBf16>(__uint_as_float(o0[c + 6]) * inv_l, __uint_as_float(o0[c + 7]) * inv_l));
-          st_shared_v4(row_addr + ((((c >> 3) + 4) ^ sw) << 4),
-                       pack2<kBf16>(__uint_as_float(o1[c + 0]) * inv_l, __uint_as_float(o1[c + 1]) * inv_l),
-                       pack2<kBf16>(__uint_as_float(o1[c + 2]) * inv_l, __uint_as_float(o1[c + 3]) * inv_l),
-                       pack2<kBf16>(__uint_as_float(o1[c + 4]) * inv_l, __uint_as_float(o1[c + 5]) * inv_l),
-                       pack2<kBf16>(__uint_as_float(o1[c + 6]) * inv_l, __uint_as_float(o1[c + 7]) * inv_l));
-        }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0 && tile_row0 + wq * 32 < S) {
-          tma_store_4d(&maps.o, stage, 0, tile_row0 + wq * 32, h, b);
-          tma_store_commit();
-        }
+        const int wq = warp & 3;
+        store_o_rows<kD, kBf16>(tO, inv_l, sStage + t * kStageBytesSp + wq * 4096, lane, &maps.o,
+                                tile_row0 + wq * 32, h, b, tile_row0 + wq * 32 < S);
       }
       if (p.lse != nullptr && row < S)
         p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);

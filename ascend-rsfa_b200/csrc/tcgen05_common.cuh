@@ -185,6 +185,52 @@ __device__ __noinline__ uint64_t softmax_half_careful(uint32_t t_s, uint32_t t_p
   return pack_f32x2(m_used, l + (h0 + h1));
 }
 
+// Epilogue of one warp: its 32 rows of O (kCols fp32 columns in tensor memory at `t_o`, one row per
+// lane) times inv_l, as 16-bit values, to global memory.  The rows go through the warp's own 4 KB of
+// 128-byte-swizzled staging (`stage`, 1024-byte aligned) and one TMA store per 64 columns: a thread owns
+// a whole row, so direct stores would touch 32 different lines per instruction, and per-warp staging needs
+// no synchronisation wider than a warp.  `map_o` describes O with boxes of 64 columns x 32 rows; rows past
+// the end of the tensor are clipped by the store, and `any_row` = false (all 32 rows past the end) stores
+// nothing.  All 32 lanes call it together; the caller waits for the stores before the CTA exits
+// (tma_store_wait_all by lane 0).
+template <int kCols, bool kBf16>
+__device__ __forceinline__ void store_o_rows(uint32_t t_o, float inv_l, uint32_t stage, int lane,
+                                             const CUtensorMap* map_o, int row_first, int h, int b, bool any_row) {
+  const bool issuer = (lane == 0);
+#pragma unroll 1
+  for (int c0 = 0; c0 < kCols; c0 += 64) {
+    uint32_t o0[32], o1[32];
+    tmem_ld_x32(t_o + c0, o0);
+    tmem_ld_x32(t_o + c0 + 32, o1);
+    tmem_wait_ld();
+    reg_fence_x32(o0);
+    reg_fence_x32(o1);
+    if (issuer) tma_store_wait_read();   // this warp's previous store no longer reads its staging rows
+    __syncwarp();
+    const uint32_t row_addr = stage + lane * 128;
+    const uint32_t sw = static_cast<uint32_t>(lane & 7);
+#pragma unroll
+    for (int c = 0; c < 32; c += 8) {
+      st_shared_v4(row_addr + (((c >> 3) ^ sw) << 4),
+                   pack2<kBf16>(__uint_as_float(o0[c + 0]) * inv_l, __uint_as_float(o0[c + 1]) * inv_l),
+                   pack2<kBf16>(__uint_as_float(o0[c + 2]) * inv_l, __uint_as_float(o0[c + 3]) * inv_l),
+                   pack2<kBf16>(__uint_as_float(o0[c + 4]) * inv_l, __uint_as_float(o0[c + 5]) * inv_l),
+                   pack2<kBf16>(__uint_as_float(o0[c + 6]) * inv_l, __uint_as_float(o0[c + 7]) * inv_l));
+      st_shared_v4(row_addr + ((((c >> 3) + 4) ^ sw) << 4),
+                   pack2<kBf16>(__uint_as_float(o1[c + 0]) * inv_l, __uint_as_float(o1[c + 1]) * inv_l),
+                   pack2<kBf16>(__uint_as_float(o1[c + 2]) * inv_l, __uint_as_float(o1[c + 3]) * inv_l),
+                   pack2<kBf16>(__uint_as_float(o1[c + 4]) * inv_l, __uint_as_float(o1[c + 5]) * inv_l),
+                   pack2<kBf16>(__uint_as_float(o1[c + 6]) * inv_l, __uint_as_float(o1[c + 7]) * inv_l));
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (issuer && any_row) {
+      tma_store_4d(map_o, stage, c0, row_first, h, b);
+      tma_store_commit();
+    }
+  }
+}
+
 // Register budgets per warpgroup after the common set-up of the 384-thread kernels (the launch
 // allocates 168 per thread): two softmax warpgroups and the warpgroup of the TMA / MMA warps.
 // setmaxnreg.inc can only take registers that another warpgroup of the same CTA has released with
