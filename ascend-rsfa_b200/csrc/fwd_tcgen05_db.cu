@@ -38,14 +38,26 @@ struct DbCfg {
   // A ring slot holds a PAIR of tiles that the MMA warps consume together: (K_0, K_1) first,
   // then (V_j, K_{j+2}) for j = 0, 1, ... - one full/empty barrier pair per slot.
   static constexpr int kSlotBytes = 2 * kKvBytes;
-  static constexpr int kStages = (D == 256) ? 2 : (D == 128 ? 4 : 6);
+  static constexpr int kStages = (D == 256) ? 3 : (D == 128 ? 4 : 6);
   static constexpr int kThreads = 32 * (4 * NT + 1 + NT);
   static constexpr int kTmaWarp = 4 * NT;
   static constexpr int kMmaWarp0 = 4 * NT + 1;   // one MMA warp per Q tile
   // q_full, q_empty, pv_done, o_full per tile; s_full, p_full per (tile, buffer); ring; scheduler
-  static constexpr int kStageBytes = kRowsDb * 128;   // epilogue staging: 128 rows x 64 columns
-  static constexpr int kNumBarriers = 4 * NT + 4 * NT + NT + 2 * kStages + 4;
-  static constexpr int kSmemBytes = NT * kQTileBytes + kStages * kSlotBytes + NT * kStageBytes + 1024 + kNumBarriers * 8 + 128;
+  // epilogue staging: 128 rows x 64 columns, twice at D = 256 (four chunks per row; the shared
+  // memory is there once Q has no buffer of its own)
+  static constexpr int kStageBufs = (D == 256) ? 2 : 1;
+  static constexpr int kStageBytes = kStageBufs * kRowsDb * 128;
+  static constexpr int kNumBarriers = 4 * NT + 4 * NT + NT + 2 * kStages + 4 + NT;
+  // D = 256 leaves 128 tensor-memory columns free: Q lives there as the A operand of QK^T.  Those
+  // MMAs then read only K from shared memory (with both operands there, N = 64 took 65 clk instead
+  // of 32 and the MMA warp was the limit), and Q needs no shared-memory buffer of its own: it comes
+  // through the ring as the first entry of a work item and its 64 KB are a third ring slot (with two
+  // slots the delivery of the K/V pairs was the next limit).
+  static constexpr bool kQTmem = (D == 256);
+  static constexpr int kQSmemBytes = kQTmem ? 0 : NT * kQTileBytes;
+  __host__ __device__ static constexpr int col_q() { return 128 * NT + D * NT; }
+  static_assert(!kQTmem || (NT == 1 && kQTileBytes == kSlotBytes), "Q travels through a ring slot");
+  static constexpr int kSmemBytes = kQSmemBytes + kStages * kSlotBytes + NT * kStageBytes + 1024 + kNumBarriers * 8 + 128;
   __host__ __device__ static constexpr int col_s(int t, int b) { return 128 * t + 64 * b; }
   __host__ __device__ static constexpr int col_o(int t) { return 128 * NT + D * t; }
 };
@@ -63,7 +75,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = smem_base;
-  const uint32_t sKV = sQ + NT * C::kQTileBytes;
+  const uint32_t sKV = sQ + C::kQSmemBytes;
   const uint32_t sStage = sKV + C::kStages * C::kSlotBytes;   // one staging buffer per softmax group
   const uint32_t sBar = sStage + NT * C::kStageBytes;
   auto bar_q_full = [&](int t) { return sBar + 8u * t; };
@@ -76,6 +88,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   auto bar_kv_empty = [&](int s) { return sBar + 8u * (8 * NT + C::kStages + s); };
   const uint32_t bar_sched_full0 = sBar + 8u * (9 * NT + 2 * C::kStages);  // 2 slots
   const uint32_t bar_sched_empty0 = bar_sched_full0 + 16u;                 // 2 slots
+  auto bar_q_tmem = [&](int t) { return bar_sched_empty0 + 16u + 8u * t; };   // Q_t converted into tensor memory
   const uint32_t misc = sBar + 8u * C::kNumBarriers;
   uint8_t* misc_ptr = smem_raw + (misc - smem_u32(smem_raw));
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(misc_ptr);
@@ -91,6 +104,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     for (int t = 0; t < NT; ++t) {
       mbar_init(bar_q_full(t), 1);
       mbar_init(bar_q_empty(t), 1);
+      mbar_init(bar_q_tmem(t), kRowsDb);
       mbar_init(bar_pv_done(t), 1);
       mbar_init(bar_o_full(t), 1);
       for (int b = 0; b < 2; ++b) {
@@ -170,10 +184,22 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           ++kv_count;
           return true;
         };
+        if constexpr (C::kQTmem) {
+          // Q is the first ring entry of the item
+          const uint32_t s = kv_count % C::kStages;
+          const uint32_t ph = (kv_count / C::kStages) & 1;
+          ok = mbar_wait(bar_kv_empty(s), ph ^ 1, abort_flag, wait_ns, kTagKvEmpty);
+          if (!ok) break;
+          RSFA_TRACE_EV(0x100);
+          mbar_arrive_expect_tx(bar_kv_full(s), C::kQTileBytes);
+          for (int bx = 0; bx < C::kBoxes; ++bx)
+            tma_load_4d(sKV + s * C::kSlotBytes + bx * C::kQBoxBytes, &maps.q, bar_kv_full(s), bx * 64, row0, h, b);
+          ++kv_count;
+        }
         // (K_0, K_1) before the Q tiles: ring slots free up while the previous item drains,
         // whereas a Q buffer is released only when that item's last QK^T on it has finished.
         ok = load_pair(&maps.k, 0, nmax > 1, 1);
-        for (int t = 0; ok && t < NT; ++t) {
+        for (int t = 0; !C::kQTmem && ok && t < NT; ++t) {
           ok = mbar_wait(bar_q_empty(t), (item_count & 1) ^ 1, abort_flag, wait_ns, kTagQEmpty);
           if (!ok) break;
           RSFA_TRACE_EV(0x100 + t);
@@ -234,7 +260,10 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t off_q = ((ks >> 2) * C::kQBoxBytes + (ks & 3) * 32) >> 4;
             const uint32_t off_k = ((ks >> 2) * C::kKvBoxBytes + (ks & 3) * 32) >> 4;
-            umma_ss(tmem_u + C::col_s(t, buf), desc_q + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
+            if constexpr (C::kQTmem)
+              umma_ts(tmem_u + C::col_s(t, buf), tmem_u + C::col_q() + ks * 8, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
+            else
+              umma_ss(tmem_u + C::col_s(t, buf), desc_q + off_q, kd + off_k, idesc_qk, ks > 0 ? 1u : 0u);
           }
           if (commit_a != 0) umma_commit(commit_a);
           if (commit_b != 0) umma_commit(commit_b);
@@ -256,8 +285,14 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         __syncwarp();
       };
 
-      ok = wait_all(bar_q_full(t), item_count & 1, kTagQFull);
+      ok = wait_all(C::kQTmem ? bar_q_tmem(t) : bar_q_full(t), item_count & 1, kTagQFull);
       if (!ok) break;
+      if constexpr (C::kQTmem) {
+        // the softmax warps have copied Q out of its ring slot: hand the slot back
+        if (lane == 0) mbar_arrive(bar_kv_empty(kv_count % C::kStages));
+        __syncwarp();
+        ++kv_count;
+      }
       // entry 0: (K_0, K_1) -> S_t[0], S_t[1]
       {
         const uint32_t s = kv_count % C::kStages;
@@ -268,7 +303,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           if (j < n) issue_qk(j, s * C::kSlotBytes + j * C::kKvBytes, bar_s_full(t, j), 0u);
         }
         // Q_t is dead after its last QK^T
-        umma_commit2_elect(n <= 2 ? bar_q_empty(t) : 0u, bar_kv_empty(s));
+        umma_commit2_elect((n <= 2 && !C::kQTmem) ? bar_q_empty(t) : 0u, bar_kv_empty(s));
         ++kv_count;
       }
       // entry j + 1: (V_j, K_{j+2})
@@ -289,7 +324,8 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         }
         if (j + 2 < n) {
           // S_t[buf] is free: PV above consumed P_j in order
-          issue_qk(buf, s * C::kSlotBytes + C::kKvBytes, bar_s_full(t, buf), j + 3 == n ? bar_q_empty(t) : 0u);
+          issue_qk(buf, s * C::kSlotBytes + C::kKvBytes, bar_s_full(t, buf),
+                   (j + 3 == n && !C::kQTmem) ? bar_q_empty(t) : 0u);
           RSFA_TRACE_EV(0x5000 + j);   // QK(j+2) issued
         }
         umma_commit_elect(bar_kv_empty(s));
@@ -307,6 +343,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     const float scale_log2 = p.sm_scale * kLog2e;
     const float headroom = kHeadroomLog2 / scale_log2;   // in raw score units (sm_scale > 0 on this path)
     uint32_t item_count = 0, o_count = 0, pv_count = 0;
+    uint32_t ring_count = 0;   // D = 256: ring entries consumed so far (to find the slot that holds Q)
     uint32_t s_count[2] = {0, 0};
     bool ok = true;
 #ifdef RSFA_TRACE
@@ -314,6 +351,34 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
                                         ? p.trace + t * 2 * kTraceCap : nullptr;
     int trace_n = 0;
 #endif
+    // D = 256: Q of a work item from its ring slot (128-byte-swizzled boxes of 64 columns) into
+    // tensor memory as the A operand of QK^T: lane = row, 32-bit column c = elements 2c, 2c+1.
+    // The caller knows that the MMAs which read the previous item's Q are complete.  The MMA warp
+    // hands the ring slot back when it sees the copy done.  `n_item` = key tiles of that item.
+    bool q_copied = false;   // the next item's Q is in tensor memory already
+    auto copy_q = [&](int n_item) -> bool {
+      const uint32_t q_slot = ring_count % C::kStages;
+      bool r = mbar_wait(bar_kv_full(q_slot), (ring_count / C::kStages) & 1, abort_flag, wait_ns, kTagQFull);
+      r = __all_sync(0xffffffffu, r);
+      if (!r) return false;
+      ring_count += 2 + n_item;   // ring entries of the item: Q, (K_0, K_1), and one per key tile
+      const uint32_t tQ = tmem_base + lane_base + C::col_q();
+      const uint32_t q_row = sKV + q_slot * C::kSlotBytes + row_in_tile * 128;
+      const uint32_t sw = static_cast<uint32_t>(row_in_tile & 7);
+#pragma unroll 1
+      for (int bx = 0; bx < C::kBoxes; ++bx) {
+        uint32_t r4[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          ld_shared_v4(q_row + bx * C::kQBoxBytes + ((static_cast<uint32_t>(c) ^ sw) << 4), r4[4 * c], r4[4 * c + 1],
+                       r4[4 * c + 2], r4[4 * c + 3]);
+        tmem_st_x32(tQ + bx * 32, r4);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(bar_q_tmem(t));
+      return true;
+    };
     while (ok) {
       const int slot = item_count & 1;
       ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
@@ -329,6 +394,11 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       const int tile_row0 = row0 + t * kRowsDb;
       const int row = tile_row0 + row_in_tile;
       const int n = num_kv_tiles_db(tile_row0, S, p.causal);
+      if constexpr (C::kQTmem) {
+        if (!q_copied) ok = copy_q(n);
+        q_copied = false;
+        if (!ok) break;
+      }
       if (n == 0) continue;
 
       // As in the 128-key kernel: the row's reference is set from the first key tile (plus
@@ -447,6 +517,23 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       }
       if (!ok) break;
       pv_count += n;
+      if constexpr (C::kQTmem) {
+        // Every QK^T of this item is complete (its last S tile was read above), so the Q columns are
+        // free: when the next work item is known already, bring its Q in now, and the MMA warp
+        // issues that item's first QK^T while this group is busy with the epilogue below.
+        const int nslot = item_count & 1;
+        const bool known = mbar_test_wait(bar_sched_full0 + 8u * nslot, (item_count >> 1) & 1);
+        if (__all_sync(0xffffffffu, known)) {
+          const int nitem = sched_ring[nslot];
+          if (nitem < sched.total_items) {
+            int nbh, nrow0;
+            decode(nitem, nbh, nrow0);
+            ok = copy_q(num_kv_tiles_db(nrow0 + t * kRowsDb, S, p.causal));
+            if (!ok) break;
+            q_copied = true;
+          }
+        }
+      }
 
       // ---- epilogue: O_t / l -> global, lse = m + log l (natural log; :400-404)
       ok = mbar_wait(bar_o_full(t), o_count & 1, abort_flag, wait_ns, kTagOFull);
@@ -460,8 +547,8 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       // O_t / l -> global memory: each warp stages and stores its own 32 rows (store_o_rows)
       {
         const int wq = warp & 3;
-        store_o_rows<D, kBf16>(tO, inv_l, sStage + t * C::kStageBytes + wq * 4096, lane, &maps.o, tile_row0 + wq * 32, h, b,
-                               tile_row0 + wq * 32 < S);
+        store_o_rows<D, kBf16, C::kStageBufs>(tO, inv_l, sStage + t * C::kStageBytes + wq * (4096 * C::kStageBufs), lane,
+                                              &maps.o, tile_row0 + wq * 32, h, b, tile_row0 + wq * 32 < S);
       }
       if (p.lse != nullptr && row < S)
         p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);

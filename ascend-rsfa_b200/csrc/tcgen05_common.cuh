@@ -192,8 +192,9 @@ __device__ __noinline__ uint64_t softmax_half_careful(uint32_t t_s, uint32_t t_p
 // no synchronisation wider than a warp.  `map_o` describes O with boxes of 64 columns x 32 rows; rows past
 // the end of the tensor are clipped by the store, and `any_row` = false (all 32 rows past the end) stores
 // nothing.  All 32 lanes call it together; the caller waits for the stores before the CTA exits
-// (tma_store_wait_all by lane 0).
-template <int kCols, bool kBf16>
+// (tma_store_wait_all by lane 0).  kBufs = 2: `stage` holds two such 4 KB buffers used in turn, so that
+// a store reads one while the next 64 columns are written to the other.
+template <int kCols, bool kBf16, int kBufs = 1>
 __device__ __forceinline__ void store_o_rows(uint32_t t_o, float inv_l, uint32_t stage, int lane,
                                              const CUtensorMap* map_o, int row_first, int h, int b, bool any_row) {
   const bool issuer = (lane == 0);
@@ -205,9 +206,11 @@ __device__ __forceinline__ void store_o_rows(uint32_t t_o, float inv_l, uint32_t
     tmem_wait_ld();
     reg_fence_x32(o0);
     reg_fence_x32(o1);
-    if (issuer) tma_store_wait_read();   // this warp's previous store no longer reads its staging rows
+    // the store that last read this staging buffer is done with it
+    if (issuer) tma_store_wait_read_but<kBufs - 1>();
     __syncwarp();
-    const uint32_t row_addr = stage + lane * 128;
+    const uint32_t buf = stage + (kBufs == 1 ? 0u : static_cast<uint32_t>((c0 >> 6) % kBufs) * 4096u);
+    const uint32_t row_addr = buf + lane * 128;
     const uint32_t sw = static_cast<uint32_t>(lane & 7);
 #pragma unroll
     for (int c = 0; c < 32; c += 8) {
@@ -225,7 +228,7 @@ __device__ __forceinline__ void store_o_rows(uint32_t t_o, float inv_l, uint32_t
     fence_proxy_async();
     __syncwarp();
     if (issuer && any_row) {
-      tma_store_4d(map_o, stage, c0, row_first, h, b);
+      tma_store_4d(map_o, buf, c0, row_first, h, b);
       tma_store_commit();
     }
   }
