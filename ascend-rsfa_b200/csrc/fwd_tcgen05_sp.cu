@@ -23,7 +23,8 @@
 // the scheme).  Because S_t is gone by the time the sum check can fail, this kernel cannot redo a
 // tile: a failed check marks the work item in `redo_flags`, the item's output is left undefined,
 // and the launcher runs the marked items again with the 128-key kernel of fwd_tcgen05.cu, which
-// can.
+// can.  When many items fail (more than one in kBailOneIn of those started), the producer warps
+// move the rest of the queue to the redo list uncomputed.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -42,6 +43,8 @@ constexpr int kThreadsSp = 384;
 constexpr int kTmaWarpSp = 8;
 constexpr int kMmaWarpSp0 = 9;  // warps 9, 10: one issuer per Q tile
 constexpr int kStagesSp = 6;
+constexpr int kBailOneIn = 8;        // give up on this kernel when more than 1 item in 8 has to be redone
+constexpr int kBailRounds = 2;       // ... but not before every CTA has started this many items
 constexpr int kQBytes = kRows * kD * 2;      // 16 KB
 constexpr int kKvBytes = kKeys * kD * 2;     // 16 KB
 constexpr int kStageBytesSp = kRows * 128;   // epilogue staging per Q tile: 128 rows x 64 columns
@@ -148,9 +151,22 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         bool ok = true;
         while (ok) {
           const int slot = item_count & 1;
+          // (read before the wait below, which hides the latency of the load)
+          int failed = *static_cast<volatile int*>(p.redo_count);
           ok = mbar_wait(bar_sched_empty0 + 8u * slot, ((item_count >> 1) & 1) ^ 1, abort_flag, wait_ns, kTagSched);
           if (!ok) break;
-          const int item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
+          // Next work item.  When more than one item in kBailOneIn has failed its sum check so far
+          // (rows close to one-hot: the data do not suit this kernel), the rest of the queue is not
+          // computed here at all but put on the redo list at once, so that the launch costs little
+          // more than the 128-key kernel alone would have.  The first kBailRounds items of every CTA always run.
+          int item;
+          for (;;) {
+            item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
+            if (item >= sched.total_items || item < kBailRounds * static_cast<int>(gridDim.x)) break;
+            if (failed * kBailOneIn <= item) break;
+            if (atomicExch(&p.redo_flags[item], 1) == 0) p.redo_list[atomicAdd(p.redo_count, 1)] = item;
+            failed = *static_cast<volatile int*>(p.redo_count);
+          }
           sched_ring[slot] = item;
           __threadfence_block();
           mbar_arrive(bar_sched_full0 + 8u * slot);

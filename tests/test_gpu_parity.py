@@ -157,6 +157,15 @@ def test_separate_p_kernel_marks_items_and_they_are_run_again(fa, cuda_device):
     assert fa.launch_count() - n0 == 6
 
 
+def test_separate_p_kernel_gives_up_on_a_batch_of_one_hot_rows(fa, cuda_device):
+    # 512 work items, more than two per CTA: once more than one item in eight has failed its sum
+    # check, the separate-P kernel puts the rest of its queue on the redo list without computing
+    # it.  Every item must still come out right, whichever of the two kernels produced it.
+    q, k, v = make_inputs(4, 64, 512, 64, seed=37)
+    check(fa, q, k, v, False, 3.0, 128, 128, cuda_device)
+    check(fa, q, k, v, True, 3.0, 128, 128, cuda_device)
+
+
 def test_result_does_not_depend_on_requested_tile(fa, cuda_device):
     """Requests that resolve to the same instantiated tile are bit-identical; different tiles agree
     within the tolerance (the reference's results are tile-independent in the same sense)."""
