@@ -638,8 +638,11 @@ cudaError_t launch_one(const FwdParams& p, int sm_count, cudaStream_t stream, lo
 
 }  // namespace
 
+// D = 16 and 32 run on the D = 64 kernels: the tensor maps describe the real D columns, the 64-column
+// boxes read zeros past them (Q, K: nothing added to the scores; V: output columns that the clipped
+// store never writes), so the kernels need no variant of their own.
 bool tcgen05_supports(int S, int D, float sm_scale) {
-  return (D == 64 || D == 128 || D == 256) && S >= 1 && sm_scale > 0.f;
+  return (D == 16 || D == 32 || D == 64 || D == 128 || D == 256) && S >= 1 && sm_scale > 0.f;
 }
 
 namespace {
@@ -652,6 +655,7 @@ const TileRow kTileTable[] = {
 }  // namespace
 
 void tcgen05_resolve_tile(int S, int D, int causal, int req_bm, int req_bn, int variant, int* bm, int* bn) {
+  if (D < 64) D = 64;   // served by the D = 64 kernels
   *bm = 128;
   if (D == 256) {  // one instantiation only
     *bn = 64;
@@ -680,8 +684,8 @@ cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t st
   if (p.tile_n == 64 || p.D == 256) return launch_fwd_tcgen05_db(p, sm_count, stream, launches);
   if (p.D == 128) return p.bf16 ? launch_one<128, true>(p, sm_count, stream, launches)
                                 : launch_one<128, false>(p, sm_count, stream, launches);
-  if (p.D == 64) {
-    // D = 64: the separate-P kernel first (it marks the work items whose sum check failed and leaves
+  if (p.D <= 64) {
+    // D = 64 (and below): the separate-P kernel first (it marks the work items whose sum check failed and leaves
     // their output undefined), then this file's kernel over the marked items only; that second
     // launch returns at once when there are none.  Without scratch for the marks, or when single-
     // buffered S is forced, this file's kernel does everything.

@@ -600,7 +600,7 @@ cudaError_t launch_db(const FwdParams& p, int sm_count, cudaStream_t stream, lon
 }  // namespace
 
 cudaError_t launch_fwd_tcgen05_db(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches) {
-  switch (p.D) {
+  switch (p.D < 64 ? 64 : p.D) {
     case 64: return p.bf16 ? launch_db<64, 2, true>(p, sm_count, stream, launches) : launch_db<64, 2, false>(p, sm_count, stream, launches);
     case 128: return p.bf16 ? launch_db<128, 2, true>(p, sm_count, stream, launches) : launch_db<128, 2, false>(p, sm_count, stream, launches);
     case 256: return p.bf16 ? launch_db<256, 1, true>(p, sm_count, stream, launches) : launch_db<256, 1, false>(p, sm_count, stream, launches);

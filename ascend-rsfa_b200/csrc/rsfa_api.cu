@@ -98,7 +98,7 @@ int choose_path(int S, int D, float sm_scale, long long heads) {
   if (forced == RSFA_PATH_TCGEN05 && tc_ok) return RSFA_PATH_TCGEN05;
   if (!tc_ok) return RSFA_PATH_GENERIC;
   if (S > 128) return RSFA_PATH_TCGEN05;
-  return (heads >= kShortSeqHeads && !(S <= 64 && D == 64)) ? RSFA_PATH_TCGEN05 : RSFA_PATH_GENERIC;
+  return (heads >= kShortSeqHeads && !(S <= 64 && D <= 64)) ? RSFA_PATH_TCGEN05 : RSFA_PATH_GENERIC;
 }
 
 // Tile a call runs: on the tcgen05 path the request is honoured when instantiated, otherwise the
@@ -296,7 +296,7 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
     tile_of_path(path, S, D, causal, block_m, block_n, &bm, &bn);
     p.tile_n = bn;
   }
-  if (path == RSFA_PATH_TCGEN05 && D == 64 && p.tile_n == 128 && p.variant != 0 &&
+  if (path == RSFA_PATH_TCGEN05 && D <= 64 && p.tile_n == 128 && p.variant != 0 &&
       rsfa::tcgen05_sp_items(p) <= kRedoCapacity) {
     std::lock_guard<std::mutex> lock(g_mu);
     if (d->redo == nullptr) {

@@ -94,7 +94,7 @@ RSFA_API int rsfa_fwd_host(const void* q_host, const void* k_host, const void* v
  * process exits) and calls no cudaMalloc, cudaFree or other allocating routine.
  *
  * Arguments as rsfa_fwd, without block_m / block_n (the kernel has one tile).  Limits: only
- * shapes the tcgen05 kernels are built for (D in {64, 128, 256}, sm_scale > 0) -> otherwise
+ * shapes the tcgen05 kernels are built for (sm_scale > 0; D = 16 and 32 run on the D = 64 kernel) -> otherwise
  * RSFA_ERR_UNSUPPORTED; at most 2^30 work items (B * H * ceil(S / 256), or ceil(S / 128) at D = 256), because the queue counter
  * is a single 32-bit word of the block -> otherwise RSFA_ERR_TOO_LARGE.
  *
@@ -122,7 +122,7 @@ RSFA_API int rsfa_get_tiling(int B, int H, int S, int D, int causal, int* block_
  * (after snapping block_m/block_n).  Counterpart of the dispatch in _attention.forward (:564-610).
  * tile_m / tile_n may be NULL.  The call carries no batch size: for S <= 128 it answers for a
  * small batch (the short-sequence kernel); rsfa_fwd sends batches of 256 heads or more of such
- * sequences to the tcgen05 kernel where that is instantiated (except S <= 64 at D = 64).
+ * sequences to the tcgen05 kernel where that is instantiated (except S <= 64 at D <= 64).
  */
 RSFA_API int rsfa_select_path(int S, int D, int causal, float sm_scale, int block_m, int block_n, int dtype,
                      int* path, int* tile_m, int* tile_n);

@@ -95,6 +95,24 @@ def test_every_head_dim(fa, cuda_device, D, causal):
     check(fa, q, k, v, causal, 1.0 / math.sqrt(D), 128, 128, cuda_device)
 
 
+@pytest.mark.parametrize("D", [16, 32])
+@pytest.mark.parametrize("variant", [0, 1, 2])
+def test_small_head_dims_on_the_d64_kernels(fa, cuda_device, D, variant):
+    # D = 16 and 32 run on the three D = 64 tcgen05 kernels (single-buffered S, double-buffered S,
+    # separate P) with zero columns read past D: every kernel, ragged lengths, both masks, bf16.
+    assert fa.select_path(300, D, True, 0.25)[0] == 1
+    fa.set_option("tcgen05_variant", variant)
+    try:
+        for S in (129, 300, 1000, 2049):
+            q, k, v = make_inputs(2, 2, S, D, seed=S + D)
+            check(fa, q, k, v, False, 0.25, 128, 128, cuda_device)
+            check(fa, q, k, v, True, 0.25, 128, 128, cuda_device)
+        q, k, v = make_inputs(1, 3, 640, D, seed=23, std=0.5, dtype=torch.bfloat16)
+        check(fa, q, k, v, True, 0.5, 128, 128, cuda_device, tol=2e-2)
+    finally:
+        fa.set_option("tcgen05_variant", -1)
+
+
 @pytest.mark.parametrize("S", [1, 7, 63, 65, 127, 129, 255, 257, 300, 511, 640, 1000])
 @pytest.mark.parametrize("D", [64, 128, 256])
 @pytest.mark.parametrize("causal", [False, True])

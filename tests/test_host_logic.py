@@ -46,7 +46,8 @@ def test_path_selection_follows_the_short_sequence_rule():
     assert fa.select_path(128, 64, False, 0.5)[0] == _capi.RSFA_PATH_GENERIC     # N_CTX <= 128 (:564)
     assert fa.select_path(2048, 128, True, 0.5)[0] == _capi.RSFA_PATH_TCGEN05
     assert fa.select_path(8192, 64, False, 0.125)[0] == _capi.RSFA_PATH_TCGEN05
-    assert fa.select_path(2048, 32, False, 0.5)[0] == _capi.RSFA_PATH_GENERIC    # D = 32 not on tcgen05
+    assert fa.select_path(2048, 32, False, 0.5)[0] == _capi.RSFA_PATH_TCGEN05    # D = 32: the D = 64 kernel
+    assert fa.select_path(128, 32, False, 0.5)[0] == _capi.RSFA_PATH_GENERIC
     assert fa.select_path(2048, 128, False, -0.5)[0] == _capi.RSFA_PATH_GENERIC  # non-positive scale
     assert fa.select_path(2048, 128, False, 0.5) == (1, 128, 128)
     # an instantiated tile is honoured, anything else is replaced by the table's row
@@ -124,13 +125,14 @@ def test_shard_is_a_view():
 
 def test_tile_table_is_total_and_consistent():
     """Every (S, D, causal) on the tcgen05 path resolves to an instantiated tile, bucket edges included."""
-    for D in (64, 128, 256):
+    for D in (16, 32, 64, 128, 256):
         for causal in (False, True):
             for S in (129, 130, 767, 768, 1535, 1536, 2048, 3071, 3072, 6143, 6144, 8192, 65536, 1 << 20):
                 bm, bn = fa.get_tiling(2, 3, S, D, causal)
                 assert bm == 128 and bn in ((64,) if D == 256 else (64, 128)), (S, D, causal, bm, bn)
                 assert fa.select_path(S, D, causal, 0.1, bm, bn) == (1, bm, bn)
     for D in (16, 32):
-        assert fa.get_tiling(1, 1, 4096, D, True) == (64, 64)      # generic kernel only
+        assert fa.get_tiling(1, 1, 4096, D, True) == fa.get_tiling(1, 1, 4096, 64, True)   # the D = 64 kernels' tiles
+        assert fa.get_tiling(1, 1, 100, D, True) == (64, 64)                              # short-sequence path
     for S in (1, 64, 128):
         assert fa.get_tiling(1, 1, S, 128, False) == (64, 64)      # short-sequence path

@@ -26,7 +26,8 @@ def _strides(*tensors):
     return (ctypes.c_int64 * 16)(*flat)
 
 
-@pytest.mark.parametrize("B,H,S,D,causal,scale", [(2, 3, 1024, 128, True, 0.5), (1, 4, 777, 64, False, 0.125)])
+@pytest.mark.parametrize("B,H,S,D,causal,scale", [(2, 3, 1024, 128, True, 0.5), (1, 4, 777, 64, False, 0.125),
+                                                  (2, 2, 600, 32, True, 0.25)])
 def test_noalloc_matches_regular_entry_point_twice(cuda_device, B, H, S, D, causal, scale):
     from ascend_rsfa import _capi
 
@@ -44,7 +45,7 @@ def test_noalloc_matches_regular_entry_point_twice(cuda_device, B, H, S, D, caus
     def regular():
         o = torch.empty_like(q)
         lse = torch.empty(B, H, S, dtype=torch.float32, device=dev)
-        # At D = 64 the regular entry point would pick the separate-P kernel, which needs scratch the
+        # At D <= 64 the regular entry point would pick the separate-P kernel, which needs scratch the
         # allocation-free call does not have; variant 0 keeps it on the kernel that call runs.
         assert lib.rsfa_set_option(b"tcgen05_variant", 0 if bn.value == 128 else -1) == _capi.RSFA_OK
         try:
@@ -80,14 +81,12 @@ def test_noalloc_rejects_what_it_cannot_serve(cuda_device):
 
     lib = _capi.load()
     dev = cuda_device
-    q = torch.zeros(1, 1, 256, 32, dtype=torch.float16, device=dev)
-    o = torch.empty_like(q)
-    rc = lib.rsfa_fwd_noalloc(q.data_ptr(), q.data_ptr(), q.data_ptr(), o.data_ptr(), None, 1, 1, 256, 32,
-                              _strides(q, q, q, o), 0, 0.5, _capi.RSFA_DTYPE_F16, None)
-    assert rc == _capi.RSFA_ERR_UNSUPPORTED            # D = 32 has no scratch-using kernel
     q = torch.zeros(1, 1, 256, 64, dtype=torch.float16, device=dev)
     o = torch.empty_like(q)
     st = _strides(q, q, q, o)
+    rc = lib.rsfa_fwd_noalloc(q.data_ptr(), q.data_ptr(), q.data_ptr(), o.data_ptr(), None, 1, 1, 256, 64,
+                              st, 0, -0.5, _capi.RSFA_DTYPE_F16, None)
+    assert rc == _capi.RSFA_ERR_UNSUPPORTED            # a scale that is not positive has no tcgen05 kernel
     # more work items than the 32-bit counter in the static block can hand out
     rc = lib.rsfa_fwd_noalloc(q.data_ptr(), q.data_ptr(), q.data_ptr(), o.data_ptr(), None, 1 << 15, 1 << 15,
                               512, 64, st, 0, 0.5, _capi.RSFA_DTYPE_F16, None)
