@@ -306,7 +306,8 @@ def main():
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["burst"], "unit": "TFLOP/s",
                          "frac": per_gpu / peaks["burst"],
                          "traffic": (NCU_DRAM_BYTES_PER_HEAD_S2048_D128 * n_local if (S, D) == (2048, 128) else None),
-                         "traffic_note": "scaled from an ncu capture of 128 heads of this shape; algorithmic bytes %.3e"
+                         "traffic_note": ("scaled from an ncu capture of 128 heads of this shape" if (S, D) == (2048, 128)
+                                          else "no ncu capture of this shape") + "; algorithmic bytes %.3e"
                                          % (4.0 * n_local * S * D * 2),
                          "peak_source": peaks["source"] + " cuBLAS bf16 burst; sustained %.1f" % peaks["sustained"],
                          "frac_of_sustained": (per_gpu / peaks["sustained"]) if peaks["sustained"] else None},
