@@ -88,8 +88,8 @@ bool valid_head_dim(int D) { return D == 16 || D == 32 || D == 64 || D == 128 ||
 // (26 against 28 to 33 us per call at a handful of heads).  From kShortSeqHeads heads on, the
 // tcgen05 kernel takes them too where it is instantiated: it runs such batches at the HBM rate
 // (512 x 8 heads of S = 128, D = 128: 87 us = 6.2 TB/s against 304 us), the mma.sync kernel does
-// not; only S <= 64 at D = 64 stays (72 against 85 us).  Longer sequences go to the tcgen05 kernel
-// where it is instantiated.
+// not; only S <= 64 at D <= 64 (72 against 85 us at D = 64) and D = 16 (56 against 68 us at S = 128)
+// stay.  Longer sequences go to the tcgen05 kernel where it is instantiated.
 constexpr long long kShortSeqHeads = 256;
 int choose_path(int S, int D, float sm_scale, long long heads) {
   const long long forced = g_force_path.load();
@@ -98,7 +98,7 @@ int choose_path(int S, int D, float sm_scale, long long heads) {
   if (forced == RSFA_PATH_TCGEN05 && tc_ok) return RSFA_PATH_TCGEN05;
   if (!tc_ok) return RSFA_PATH_GENERIC;
   if (S > 128) return RSFA_PATH_TCGEN05;
-  return (heads >= kShortSeqHeads && !(S <= 64 && D <= 64)) ? RSFA_PATH_TCGEN05 : RSFA_PATH_GENERIC;
+  return (heads >= kShortSeqHeads && D >= 32 && !(S <= 64 && D <= 64)) ? RSFA_PATH_TCGEN05 : RSFA_PATH_GENERIC;
 }
 
 // Tile a call runs: on the tcgen05 path the request is honoured when instantiated, otherwise the

@@ -122,7 +122,7 @@ RSFA_API int rsfa_get_tiling(int B, int H, int S, int D, int causal, int* block_
  * (after snapping block_m/block_n).  Counterpart of the dispatch in _attention.forward (:564-610).
  * tile_m / tile_n may be NULL.  The call carries no batch size: for S <= 128 it answers for a
  * small batch (the short-sequence kernel); rsfa_fwd sends batches of 256 heads or more of such
- * sequences to the tcgen05 kernel where that is instantiated (except S <= 64 at D <= 64).
+ * sequences to the tcgen05 kernel where that is instantiated (except S <= 64 at D <= 64, and D = 16).
  */
 RSFA_API int rsfa_select_path(int S, int D, int causal, float sm_scale, int block_m, int block_n, int dtype,
                      int* path, int* tile_m, int* tile_n);

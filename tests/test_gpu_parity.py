@@ -155,7 +155,8 @@ def test_large_batches_of_short_sequences_take_the_tcgen05_kernel(fa, cuda_devic
     # one work item is then a single, partly empty pair of Q tiles.  The launch counter shows
     # one launch either way (a single key tile does not use the D = 64 two-launch scheme).
     for B, H, S, D, scale in [(40, 8, 128, 128, 0.3), (33, 8, 96, 64, 0.25), (32, 8, 128, 256, 0.0625),
-                              (64, 4, 77, 128, 0.3), (64, 4, 64, 64, 0.25), (2, 4, 128, 128, 0.3)]:
+                              (64, 4, 77, 128, 0.3), (64, 4, 64, 64, 0.25), (2, 4, 128, 128, 0.3),
+                              (64, 4, 128, 32, 0.3), (33, 8, 100, 16, 0.5), (64, 4, 64, 32, 0.3)]:
         q, k, v = make_inputs(B, H, S, D, seed=S + D + B)
         n0 = fa.launch_count()
         check(fa, q, k, v, causal, scale, 128, 128, cuda_device)
