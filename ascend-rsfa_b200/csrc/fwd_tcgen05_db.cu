@@ -39,7 +39,12 @@ struct DbCfg {
   // then (V_j, K_{j+2}) for j = 0, 1, ... - one full/empty barrier pair per slot.
   static constexpr int kSlotBytes = 2 * kKvBytes;
   static constexpr int kStages = (D == 256) ? 3 : (D == 128 ? 4 : 6);
-  static constexpr int kThreads = 32 * (4 * NT + 1 + NT);
+  // D = 256 has a warpgroup of its own for the epilogue (warps 8-11; a warp reads the tensor-memory
+  // lanes 32 * (warp % 4) ...): the single softmax group goes straight on to the next work item and
+  // the O store runs beside that item's first key tiles.  Warps 6 and 7 have no role.
+  static constexpr bool kEpi = (D == 256);
+  static constexpr int kEpiWarp0 = 8;
+  static constexpr int kThreads = kEpi ? 384 : 32 * (4 * NT + 1 + NT);
   static constexpr int kTmaWarp = 4 * NT;
   static constexpr int kMmaWarp0 = 4 * NT + 1;   // one MMA warp per Q tile
   // q_full, q_empty, pv_done, o_full per tile; s_full, p_full per (tile, buffer); ring; scheduler
@@ -47,7 +52,7 @@ struct DbCfg {
   // memory is there once Q has no buffer of its own)
   static constexpr int kStageBufs = (D == 256) ? 2 : 1;
   static constexpr int kStageBytes = kStageBufs * kRowsDb * 128;
-  static constexpr int kNumBarriers = 4 * NT + 4 * NT + NT + 2 * kStages + 4 + NT;
+  static constexpr int kNumBarriers = 4 * NT + 4 * NT + NT + 2 * kStages + 4 + NT + 2;
   // D = 256 leaves 128 tensor-memory columns free: Q lives there as the A operand of QK^T.  Those
   // MMAs then read only K from shared memory (with both operands there, N = 64 took 65 clk instead
   // of 32 and the MMA warp was the limit), and Q needs no shared-memory buffer of its own: it comes
@@ -57,7 +62,7 @@ struct DbCfg {
   static constexpr int kQSmemBytes = kQTmem ? 0 : NT * kQTileBytes;
   __host__ __device__ static constexpr int col_q() { return 128 * NT + D * NT; }
   static_assert(!kQTmem || (NT == 1 && kQTileBytes == kSlotBytes), "Q travels through a ring slot");
-  static constexpr int kSmemBytes = kQSmemBytes + kStages * kSlotBytes + NT * kStageBytes + 1024 + kNumBarriers * 8 + 128;
+  static constexpr int kSmemBytes = kQSmemBytes + kStages * kSlotBytes + NT * kStageBytes + 1024 + kNumBarriers * 8 + 128 + 512;
   __host__ __device__ static constexpr int col_s(int t, int b) { return 128 * t + 64 * b; }
   __host__ __device__ static constexpr int col_o(int t) { return 128 * NT + D * t; }
 };
@@ -89,11 +94,16 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   const uint32_t bar_sched_full0 = sBar + 8u * (9 * NT + 2 * C::kStages);  // 2 slots
   const uint32_t bar_sched_empty0 = bar_sched_full0 + 16u;                 // 2 slots
   auto bar_q_tmem = [&](int t) { return bar_sched_empty0 + 16u + 8u * t; };   // Q_t converted into tensor memory
+  // D = 256: softmax group -> epilogue warps (1 / l of every row is in s_inv_l), epilogue warps -> MMA
+  // warp and softmax group (O has been read, s_inv_l may be written again)
+  const uint32_t bar_epi_ready = bar_q_tmem(NT - 1) + 8u;
+  const uint32_t bar_o_free = bar_epi_ready + 8u;
   const uint32_t misc = sBar + 8u * C::kNumBarriers;
   uint8_t* misc_ptr = smem_raw + (misc - smem_u32(smem_raw));
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(misc_ptr);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc_ptr + 4);
   volatile int* sched_ring = reinterpret_cast<volatile int*>(misc_ptr + 8);
+  volatile float* s_inv_l = reinterpret_cast<volatile float*>(misc_ptr + 128);   // kRowsDb values
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -118,8 +128,11 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_sched_full0 + 8u * s, 1);
-      mbar_init(bar_sched_empty0 + 8u * s, NT + 4 * NT);  // one lane per MMA warp and per softmax warp
+      // one lane per MMA warp, per softmax warp and per epilogue warp
+      mbar_init(bar_sched_empty0 + 8u * s, NT + 4 * NT + (C::kEpi ? 4 : 0));
     }
+    mbar_init(bar_epi_ready, kRowsDb);
+    mbar_init(bar_o_free, 4);
     fence_barrier_init();
     fence_proxy_async();
   }
@@ -153,11 +166,29 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       RSFA_TRACE_DECL(3);
       uint32_t kv_count = 0, item_count = 0;
       bool ok = true;
+      // D = 256: Q reaches the softmax warps through the ring, and at a work-item boundary everything
+      // waits for it (2 us from HBM).  So the Q tile of the NEXT item is sent on its way to L2 as early as
+      // the item is known: without the causal mask the next item is claimed while this one starts (all
+      // items take equally long, claiming one ahead costs no balance); with it, when it is claimed
+      // anyway, which is still two key tiles before its load can be issued.
+      int claimed = -1;
+      auto prefetch_q = [&](int it) {
+        if (it >= sched.total_items) return;
+        int pbh, prow0;
+        decode(it, pbh, prow0);
+        const int pb = pbh / p.H, ph = pbh - pb * p.H;
+        for (int bx = 0; bx < C::kBoxes; ++bx) tma_prefetch_l2_4d(&maps.q, bx * 64, prow0, ph, pb);
+      };
       while (ok) {
         const int slot = item_count & 1;
         ok = mbar_wait(bar_sched_empty0 + 8u * slot, ((item_count >> 1) & 1) ^ 1, abort_flag, wait_ns, kTagSched);
         if (!ok) break;
-        const int item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
+        int item = claimed;
+        claimed = -1;
+        if (item < 0) {
+          item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
+          if (C::kQTmem) prefetch_q(item);
+        }
         sched_ring[slot] = item;
         __threadfence_block();
         mbar_arrive(bar_sched_full0 + 8u * slot);
@@ -185,6 +216,10 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           return true;
         };
         if constexpr (C::kQTmem) {
+          if (!p.causal) {
+            claimed = static_cast<int>(atomicAdd(p.tile_counter, 1u));
+            prefetch_q(claimed);
+          }
           // Q is the first ring entry of the item
           const uint32_t s = kv_count % C::kStages;
           const uint32_t ph = (kv_count / C::kStages) & 1;
@@ -212,7 +247,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         ++item_count;
       }
     }
-  } else if (warp >= C::kMmaWarp0) {
+  } else if (warp >= C::kMmaWarp0 && warp < C::kMmaWarp0 + NT) {
     // ============================================================== MMA issuers, one warp per Q tile
     // Every lane runs this role with identical control flow (operands stay in uniform registers);
     // only the tcgen05 instructions are issued by one elected lane.  Both warps walk the same
@@ -287,6 +322,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
 
       ok = wait_all(C::kQTmem ? bar_q_tmem(t) : bar_q_full(t), item_count & 1, kTagQFull);
       if (!ok) break;
+      RSFA_TRACE_EV(0x4000);   // Q seen
       if constexpr (C::kQTmem) {
         // the softmax warps have copied Q out of its ring slot: hand the slot back
         if (lane == 0) mbar_arrive(bar_kv_empty(kv_count % C::kStages));
@@ -299,9 +335,11 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         ok = wait_all(bar_kv_full(s), (kv_count / C::kStages) & 1, kTagKvFull);
         if (!ok) break;
         tc_fence_after_sync();
+        RSFA_TRACE_EV(0x60ff);   // (K_0, K_1) present
         for (int j = 0; j < 2; ++j) {
           if (j < n) issue_qk(j, s * C::kSlotBytes + j * C::kKvBytes, bar_s_full(t, j), 0u);
         }
+        RSFA_TRACE_EV(0x50ff);   // QK^T 0 and 1 issued
         // Q_t is dead after its last QK^T
         umma_commit2_elect((n <= 2 && !C::kQTmem) ? bar_q_empty(t) : 0u, bar_kv_empty(s));
         ++kv_count;
@@ -319,6 +357,13 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           ++p_count[buf];
           tc_fence_after_sync();
           RSFA_TRACE_EV(0x1000 + j);   // P seen
+          if (C::kEpi && j == 0 && item_count > 0) {
+            // the first PV of an item overwrites O: the epilogue warps must have read the last one
+            ok = wait_all(bar_o_free, (item_count - 1) & 1, kTagOFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            RSFA_TRACE_EV(0x3000 + j);   // O free seen
+          }
           issue_pv(buf, s * C::kSlotBytes, j > 0, bar_pv_done(t), j == n - 1 ? bar_o_full(t) : 0u);
           RSFA_TRACE_EV(0x2000 + j);   // PV issued
         }
@@ -334,7 +379,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       if (!ok) break;
       ++item_count;
     }
-  } else {
+  } else if (warp < 4 * NT) {
     // ========================================================== softmax groups
     const int t = warp >> 2;   // Q tile of this group
     const int row_in_tile = (warp & 3) * 32 + lane;
@@ -361,6 +406,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       bool r = mbar_wait(bar_kv_full(q_slot), (ring_count / C::kStages) & 1, abort_flag, wait_ns, kTagQFull);
       r = __all_sync(0xffffffffu, r);
       if (!r) return false;
+      RSFA_TRACE_EV(0x8000);   // Q present in its ring slot
       ring_count += 2 + n_item;   // ring entries of the item: Q, (K_0, K_1), and one per key tile
       const uint32_t tQ = tmem_base + lane_base + C::col_q();
       const uint32_t q_row = sKV + q_slot * C::kSlotBytes + row_in_tile * 128;
@@ -377,6 +423,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(bar_q_tmem(t));
+      RSFA_TRACE_EV(0x9000);   // Q copied into tensor memory
       return true;
     };
     while (ok) {
@@ -517,10 +564,24 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       }
       if (!ok) break;
       pv_count += n;
+      if constexpr (C::kEpi) {
+        // ---- the epilogue warps store O: they get 1 / l; lse = m + log l is written here
+        if (o_count > 0) {   // they are done with the item before (long ago, as a rule)
+          ok = mbar_wait(bar_o_free, (o_count - 1) & 1, abort_flag, wait_ns, kTagOFull);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        ++o_count;
+        s_inv_l[row_in_tile] = 1.f / l;
+        mbar_arrive(bar_epi_ready);
+        if (p.lse != nullptr && row < S)
+          p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);
+        RSFA_TRACE_EV(0x7000);   // item handed to the epilogue warps
+      }
       if constexpr (C::kQTmem) {
         // Every QK^T of this item is complete (its last S tile was read above), so the Q columns are
         // free: when the next work item is known already, bring its Q in now, and the MMA warp
-        // issues that item's first QK^T while this group is busy with the epilogue below.
+        // issues that item's first QK^T while O is being stored.
         const int nslot = item_count & 1;
         const bool known = mbar_test_wait(bar_sched_full0 + 8u * nslot, (item_count >> 1) & 1);
         if (__all_sync(0xffffffffu, known)) {
@@ -535,6 +596,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         }
       }
 
+      if constexpr (C::kEpi) continue;
       // ---- epilogue: O_t / l -> global, lse = m + log l (natural log; :400-404)
       ok = mbar_wait(bar_o_full(t), o_count & 1, abort_flag, wait_ns, kTagOFull);
       ok = __all_sync(0xffffffffu, ok);
@@ -556,6 +618,49 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       RSFA_TRACE_EV(0x7000);   // epilogue done
     }
     if (lane == 0) tma_store_wait_all();   // the last TMA stores must be complete before the CTA exits
+  } else if (C::kEpi && warp >= C::kEpiWarp0) {
+    // ============================================================== epilogue warps (D = 256)
+    // Follow the scheduler like the other roles; per item: wait for 1 / l from the softmax group and
+    // for the last PV, store O / l (store_o_rows), tell the MMA warp that O may be overwritten.
+    const int wq = warp & 3;
+    const uint32_t tO = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + C::col_o(0);
+    uint32_t item_count = 0;
+    bool ok = true;
+    RSFA_TRACE_DECL(1);
+#ifdef RSFA_TRACE
+    if (wq != 0) trace_buf = nullptr;
+#endif
+    while (ok) {
+      const int slot = item_count & 1;
+      ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int item = sched_ring[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sched_empty0 + 8u * slot);
+      if (item >= sched.total_items) break;
+      int bh, row0;
+      decode(item, bh, row0);
+      const int b = bh / p.H, h = bh - b * p.H;
+      ok = mbar_wait(bar_epi_ready, item_count & 1, abort_flag, wait_ns, kTagOFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const float inv_l = s_inv_l[wq * 32 + lane];
+      RSFA_TRACE_EV(0xe000);   // 1 / l seen
+      ok = mbar_wait(bar_o_full(0), item_count & 1, abort_flag, wait_ns, kTagOFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      RSFA_TRACE_EV(0x6000);   // O seen
+      store_o_rows<D, kBf16, C::kStageBufs>(tO, inv_l, sStage + wq * (4096 * C::kStageBufs), lane, &maps.o, row0 + wq * 32,
+                                            h, b, row0 + wq * 32 < S);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_o_free);
+      RSFA_TRACE_EV(0x7000);   // epilogue done
+      ++item_count;
+    }
+    if (lane == 0) tma_store_wait_all();
   }
 
   // ------------------------------------------------------------------ teardown
