@@ -52,12 +52,13 @@ struct DbCfg {
   // memory is there once Q has no buffer of its own)
   static constexpr int kStageBufs = (D == 256) ? 2 : 1;
   static constexpr int kStageBytes = kStageBufs * kRowsDb * 128;
-  static constexpr int kNumBarriers = 4 * NT + 4 * NT + NT + 2 * kStages + 4 + NT + 2;
+  static constexpr int kNumBarriers = 4 * NT + 4 * NT + NT + 2 * kStages + 4 + 2;
   // D = 256 leaves 128 tensor-memory columns free: Q lives there as the A operand of QK^T.  Those
   // MMAs then read only K from shared memory (with both operands there, N = 64 took 65 clk instead
   // of 32 and the MMA warp was the limit), and Q needs no shared-memory buffer of its own: it comes
-  // through the ring as the first entry of a work item and its 64 KB are a third ring slot (with two
-  // slots the delivery of the K/V pairs was the next limit).
+  // through the ring as the first entry of a work item, the MMA warp copies it into tensor memory
+  // with tcgen05.cp, and its 64 KB are a third ring slot (with two slots the delivery of the K/V
+  // pairs was the next limit).
   static constexpr bool kQTmem = (D == 256);
   static constexpr int kQSmemBytes = kQTmem ? 0 : NT * kQTileBytes;
   __host__ __device__ static constexpr int col_q() { return 128 * NT + D * NT; }
@@ -93,10 +94,9 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   auto bar_kv_empty = [&](int s) { return sBar + 8u * (8 * NT + C::kStages + s); };
   const uint32_t bar_sched_full0 = sBar + 8u * (9 * NT + 2 * C::kStages);  // 2 slots
   const uint32_t bar_sched_empty0 = bar_sched_full0 + 16u;                 // 2 slots
-  auto bar_q_tmem = [&](int t) { return bar_sched_empty0 + 16u + 8u * t; };   // Q_t converted into tensor memory
   // D = 256: softmax group -> epilogue warps (1 / l of every row is in s_inv_l), epilogue warps -> MMA
   // warp and softmax group (O has been read, s_inv_l may be written again)
-  const uint32_t bar_epi_ready = bar_q_tmem(NT - 1) + 8u;
+  const uint32_t bar_epi_ready = bar_sched_empty0 + 16u;
   const uint32_t bar_o_free = bar_epi_ready + 8u;
   const uint32_t misc = sBar + 8u * C::kNumBarriers;
   uint8_t* misc_ptr = smem_raw + (misc - smem_u32(smem_raw));
@@ -114,7 +114,6 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     for (int t = 0; t < NT; ++t) {
       mbar_init(bar_q_full(t), 1);
       mbar_init(bar_q_empty(t), 1);
-      mbar_init(bar_q_tmem(t), kRowsDb);
       mbar_init(bar_pv_done(t), 1);
       mbar_init(bar_o_full(t), 1);
       for (int b = 0; b < 2; ++b) {
@@ -320,14 +319,28 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         __syncwarp();
       };
 
-      ok = wait_all(C::kQTmem ? bar_q_tmem(t) : bar_q_full(t), item_count & 1, kTagQFull);
-      if (!ok) break;
-      RSFA_TRACE_EV(0x4000);   // Q seen
       if constexpr (C::kQTmem) {
-        // the softmax warps have copied Q out of its ring slot: hand the slot back
-        if (lane == 0) mbar_arrive(bar_kv_empty(kv_count % C::kStages));
+        // Q arrives as the first ring entry of the item.  This warp copies it into tensor memory
+        // itself (tcgen05.cp: 16 elements of D = eight columns per instruction, the same shared-memory
+        // slabs an SS-form MMA would read); the copies run in order behind the last item's MMAs and in
+        // front of the QK^T issued below, and the slot is free again when they are complete.
+        const uint32_t qs = kv_count % C::kStages;
+        ok = wait_all(bar_kv_full(qs), (kv_count / C::kStages) & 1, kTagQFull);
+        if (!ok) break;
+        tc_fence_after_sync();
+        RSFA_TRACE_EV(0x4000);   // Q present
+        const uint64_t qd = desc_k0 + static_cast<uint64_t>((qs * C::kSlotBytes) >> 4);
+        if (elect_one()) {
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks)
+            tmem_cp_128x256b(tmem_u + C::col_q() + ks * 8, qd + (((ks >> 2) * C::kQBoxBytes + (ks & 3) * 32) >> 4));
+          umma_commit(bar_kv_empty(qs));
+        }
         __syncwarp();
         ++kv_count;
+      } else {
+        ok = wait_all(bar_q_full(t), item_count & 1, kTagQFull);
+        if (!ok) break;
       }
       // entry 0: (K_0, K_1) -> S_t[0], S_t[1]
       {
@@ -388,7 +401,6 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     const float scale_log2 = p.sm_scale * kLog2e;
     const float headroom = kHeadroomLog2 / scale_log2;   // in raw score units (sm_scale > 0 on this path)
     uint32_t item_count = 0, o_count = 0, pv_count = 0;
-    uint32_t ring_count = 0;   // D = 256: ring entries consumed so far (to find the slot that holds Q)
     uint32_t s_count[2] = {0, 0};
     bool ok = true;
 #ifdef RSFA_TRACE
@@ -396,36 +408,6 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
                                         ? p.trace + t * 2 * kTraceCap : nullptr;
     int trace_n = 0;
 #endif
-    // D = 256: Q of a work item from its ring slot (128-byte-swizzled boxes of 64 columns) into
-    // tensor memory as the A operand of QK^T: lane = row, 32-bit column c = elements 2c, 2c+1.
-    // The caller knows that the MMAs which read the previous item's Q are complete.  The MMA warp
-    // hands the ring slot back when it sees the copy done.  `n_item` = key tiles of that item.
-    bool q_copied = false;   // the next item's Q is in tensor memory already
-    auto copy_q = [&](int n_item) -> bool {
-      const uint32_t q_slot = ring_count % C::kStages;
-      bool r = mbar_wait(bar_kv_full(q_slot), (ring_count / C::kStages) & 1, abort_flag, wait_ns, kTagQFull);
-      r = __all_sync(0xffffffffu, r);
-      if (!r) return false;
-      RSFA_TRACE_EV(0x8000);   // Q present in its ring slot
-      ring_count += 2 + n_item;   // ring entries of the item: Q, (K_0, K_1), and one per key tile
-      const uint32_t tQ = tmem_base + lane_base + C::col_q();
-      const uint32_t q_row = sKV + q_slot * C::kSlotBytes + row_in_tile * 128;
-      const uint32_t sw = static_cast<uint32_t>(row_in_tile & 7);
-#pragma unroll 1
-      for (int bx = 0; bx < C::kBoxes; ++bx) {
-        uint32_t r4[32];
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          ld_shared_v4(q_row + bx * C::kQBoxBytes + ((static_cast<uint32_t>(c) ^ sw) << 4), r4[4 * c], r4[4 * c + 1],
-                       r4[4 * c + 2], r4[4 * c + 3]);
-        tmem_st_x32(tQ + bx * 32, r4);
-      }
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(bar_q_tmem(t));
-      RSFA_TRACE_EV(0x9000);   // Q copied into tensor memory
-      return true;
-    };
     while (ok) {
       const int slot = item_count & 1;
       ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
@@ -441,11 +423,6 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       const int tile_row0 = row0 + t * kRowsDb;
       const int row = tile_row0 + row_in_tile;
       const int n = num_kv_tiles_db(tile_row0, S, p.causal);
-      if constexpr (C::kQTmem) {
-        if (!q_copied) ok = copy_q(n);
-        q_copied = false;
-        if (!ok) break;
-      }
       if (n == 0) continue;
 
       // As in the 128-key kernel: the row's reference is set from the first key tile (plus
@@ -578,24 +555,6 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);
         RSFA_TRACE_EV(0x7000);   // item handed to the epilogue warps
       }
-      if constexpr (C::kQTmem) {
-        // Every QK^T of this item is complete (its last S tile was read above), so the Q columns are
-        // free: when the next work item is known already, bring its Q in now, and the MMA warp
-        // issues that item's first QK^T while O is being stored.
-        const int nslot = item_count & 1;
-        const bool known = mbar_test_wait(bar_sched_full0 + 8u * nslot, (item_count >> 1) & 1);
-        if (__all_sync(0xffffffffu, known)) {
-          const int nitem = sched_ring[nslot];
-          if (nitem < sched.total_items) {
-            int nbh, nrow0;
-            decode(nitem, nbh, nrow0);
-            ok = copy_q(num_kv_tiles_db(nrow0 + t * kRowsDb, S, p.causal));
-            if (!ok) break;
-            q_copied = true;
-          }
-        }
-      }
-
       if constexpr (C::kEpi) continue;
       // ---- epilogue: O_t / l -> global, lse = m + log l (natural log; :400-404)
       ok = mbar_wait(bar_o_full(t), o_count & 1, abort_flag, wait_ns, kTagOFull);

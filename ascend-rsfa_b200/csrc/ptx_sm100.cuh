@@ -52,21 +52,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// One look at the barrier, never suspends: true when the phase with this parity is complete.
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
 // Status codes a kernel can leave in its status word (0 = fine).
 enum : int {
   kStatusOk = 0,
@@ -172,9 +157,6 @@ __device__ __forceinline__ void tma_store_wait_read_but() {
 }
 // Wait until the bulk stores of this thread are complete.
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
-}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -235,6 +217,13 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       : "memory");
 }
 
+
+// 128 rows x 256 bits (eight 32-bit columns per lane) from shared memory, described like an MMA
+// operand, into tensor memory at [t_dst]; runs in order with the MMAs issued by the same thread and
+// is covered by the next tcgen05.commit.
+__device__ __forceinline__ void tmem_cp_128x256b(uint32_t t_dst, uint64_t s_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(t_dst), "l"(s_desc) : "memory");
+}
 
 // One lane of a converged warp.  The MMA warp keeps its control flow and operand arithmetic
 // warp-uniform (so descriptors live in uniform registers) and elects a lane only for the
