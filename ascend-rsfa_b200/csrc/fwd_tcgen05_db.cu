@@ -18,6 +18,10 @@
 // TMEM columns: S_t[b] at 128 t + 64 b, O_t at 128 kNT + D t (kNT = 2 for D <= 128, 1 for D = 256).
 // Shared memory: Q tiles + a ring of K/V tiles of 64 keys filled by TMA (128-byte swizzle).
 // Roles: warps [0, 4 kNT) softmax (one thread per row), then one TMA warp and kNT MMA warps.
+// D = 256 differs in three ways (see DbCfg): Q travels through the K/V ring and is copied into the
+// 128 spare tensor-memory columns by the MMA warp (tcgen05.cp), QK^T reads it from there (A in
+// tensor memory, only K from shared memory), and warps 8-11 do the epilogue so that the single
+// softmax group can go on to the next work item at once.
 // Work items (batch*head, block of 128 kNT rows) come from an atomic queue, head-major, causal
 // blocks heaviest first inside a head.
 #include "tcgen05_common.cuh"
