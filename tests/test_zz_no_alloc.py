@@ -27,7 +27,7 @@ def _strides(*tensors):
 
 
 @pytest.mark.parametrize("B,H,S,D,causal,scale", [(2, 3, 1024, 128, True, 0.5), (1, 4, 777, 64, False, 0.125),
-                                                  (2, 2, 600, 32, True, 0.25)])
+                                                  (2, 2, 600, 32, True, 0.25), (2, 3, 900, 256, True, 0.0625)])
 def test_noalloc_matches_regular_entry_point_twice(cuda_device, B, H, S, D, causal, scale):
     from ascend_rsfa import _capi
 
