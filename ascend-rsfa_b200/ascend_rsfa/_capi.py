@@ -38,6 +38,8 @@ SIGNATURES = {
     "rsfa_select_path": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int, _c.c_float, _c.c_int, _c.c_int,
                                     _c.c_int, _c.POINTER(_c.c_int), _c.POINTER(_c.c_int),
                                     _c.POINTER(_c.c_int)]),
+    "rsfa_work_items": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_float,
+                                   _c.POINTER(_c.c_longlong)]),
     "rsfa_sm_count": (_c.c_int, [_c.c_int]),
     "rsfa_device_status": (_c.c_int, [_c.c_int, _c.POINTER(_c.c_int)]),
     "rsfa_launch_count": (_c.c_longlong, []),

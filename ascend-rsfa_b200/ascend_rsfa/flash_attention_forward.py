@@ -176,6 +176,15 @@ def device_status(device=None):
     _capi.check(rc, "rsfa_device_status")
 
 
+def work_items(Z, H, N_CTX, HEAD_DIM, causal, sm_scale):
+    """Units of work a call is split into: (batch, head, block of query rows) items of the persistent
+    tcgen05 kernels, or CTAs of the short-sequence kernel (the reference's NUM_BLOCKS, :289-294)."""
+    n = ctypes.c_longlong(0)
+    _capi.check(_lib.rsfa_work_items(int(Z), int(H), int(N_CTX), int(HEAD_DIM), 1 if causal else 0, float(sm_scale),
+                                     ctypes.byref(n)), "rsfa_work_items")
+    return n.value
+
+
 def launch_count():
     """Kernels launched by the library in this process."""
     return int(_lib.rsfa_launch_count())

@@ -31,8 +31,17 @@ struct FwdParams {
   int* redo_list;
   int redo_capacity;   // work items the scratch has room for
   int* status;                 // device status word, never null
-  unsigned int* tile_counter;  // device work-queue counter (persistent kernel)
+  // Work queue of the persistent kernels: word [0] hands out work items, word [1] counts the CTAs
+  // that have finished.  Both are zero before a launch; the CTA that finishes last puts them back
+  // to zero, so the next launch that gets this pair needs no memset in front of it.
+  unsigned int* tile_counter;
   unsigned long long wait_limit_ns;
+  int pdl;             // 1: launch with programmatic stream serialisation (the "pdl" option)
+  // Test hook (the "test_drop_load" option, -1 = off): the producer of the 128-key tcgen05 kernel
+  // leaves out its n-th K/V tile load together with the barrier arrival that announces it.  Nothing
+  // is in flight for that tile and no address is touched; the consumer's bounded wait simply runs
+  // out, which is how the tests reach the wait-expired path on a healthy GPU.
+  int test_drop_load;
 #ifdef RSFA_TRACE
   unsigned long long* trace;  // debug builds only: per-role event log of CTA 0
 #endif
@@ -54,6 +63,8 @@ inline cudaError_t set_dynamic_smem_once(std::atomic<unsigned long long>& done, 
 // Launchers implemented in the kernel translation units.  Each returns a cudaError_t
 // from the launch itself and bumps *launches by the number of kernels it started.
 cudaError_t launch_fwd_generic(const FwdParams& p, cudaStream_t stream, long long* launches);
+// CTAs the short-sequence kernel launches: one per (batch, head, block of 64 query rows), all on grid.x.
+long long generic_grid_blocks(int B, int H, int S);
 cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t stream,
                                long long* launches);
 // The double-buffered-S family (D = 64, 128, 256), selected by launch_fwd_tcgen05.
@@ -71,6 +82,13 @@ int tcgen05_sp_items(const FwdParams& p);
 void tcgen05_resolve_tile(int S, int D, int causal, int req_bm, int req_bn, int variant, int* bm, int* bn);
 // Adds to the process-wide kernel-launch counter behind rsfa_launch_count().
 void count_launches(long long n);
+// Current values of the "wait_limit_ms" (in ns), "pdl" and "test_drop_load" options.
+unsigned long long option_wait_limit_ns();
+int option_pdl();
+int option_test_drop_load();
+// Device address of the status word in the static scratch block of rsfa_fwd_noalloc on `device`, or
+// null while that entry point has not been used there.
+int* noalloc_status_word(int device);
 // True when the tcgen05 kernel is instantiated for this head dimension.
 bool tcgen05_supports(int S, int D, float sm_scale);
 

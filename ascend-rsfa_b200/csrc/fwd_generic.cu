@@ -98,11 +98,13 @@ __global__ void __launch_bounds__(kThreads) fwd_generic_kernel(const FwdParams p
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int bh = blockIdx.y;
+  // One linear grid index = (head, row block): gridDim.y stops at 65535, the number of heads does not.
+  const int S = p.S;
+  const int row_blocks = (S + kBM - 1) / kBM;
+  const int bh = blockIdx.x / row_blocks;
   const int b = bh / p.H;
   const int h = bh % p.H;
-  const int m0 = blockIdx.x * kBM;
-  const int S = p.S;
+  const int m0 = (blockIdx.x - bh * row_blocks) * kBM;
 
   const uint16_t* gq = reinterpret_cast<const uint16_t*>(p.q) + b * p.q_stride[0] + h * p.q_stride[1];
   const uint16_t* gk = reinterpret_cast<const uint16_t*>(p.k) + b * p.k_stride[0] + h * p.k_stride[1];
@@ -250,8 +252,9 @@ cudaError_t launch_one(const FwdParams& p, cudaStream_t stream) {
   static std::atomic<unsigned long long> smem_done{0};   // per kernel instantiation, bit per device
   cudaError_t e = set_dynamic_smem_once(smem_done, reinterpret_cast<const void*>(kern), Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((p.S + kBM - 1) / kBM, p.B * p.H);
-  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(p);
+  const long long blocks = generic_grid_blocks(p.B, p.H, p.S);
+  if (blocks > 2147483647LL) return cudaErrorInvalidConfiguration;
+  kern<<<static_cast<unsigned int>(blocks), kThreads, Cfg::kSmemBytes, stream>>>(p);
   return cudaGetLastError();
 }
 
@@ -261,6 +264,10 @@ cudaError_t launch_dtype(const FwdParams& p, cudaStream_t stream) {
 }
 
 }  // namespace
+
+long long generic_grid_blocks(int B, int H, int S) {
+  return static_cast<long long>(B) * H * ((S + kBM - 1) / kBM);
+}
 
 cudaError_t launch_fwd_generic(const FwdParams& p, cudaStream_t stream, long long* launches) {
   cudaError_t e;

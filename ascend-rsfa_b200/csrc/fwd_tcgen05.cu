@@ -116,8 +116,12 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint64_t wait_ns = p.wait_limit_ns;
-  // Redo mode with nothing to redo (the usual case): leave before anything is set up.
-  if (sched.redo_count != nullptr && *reinterpret_cast<const volatile int*>(sched.redo_count) == 0) return;
+  // Redo mode with nothing to redo (the usual case): leave before anything is set up.  The count is
+  // written by the kernel in front of this one, so it is read only once that kernel has completed.
+  if (sched.redo_count != nullptr) {
+    griddep_wait();
+    if (*reinterpret_cast<const volatile int*>(sched.redo_count) == 0) return;
+  }
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -155,6 +159,9 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
+  // Everything above touched only this CTA's shared and tensor memory; from here on global memory
+  // is read and written, which has to wait for the kernel in front of this one on the stream.
+  griddep_wait();
 
   const int S = p.S;
   const int items_per_head = sched.items_per_head;
@@ -191,7 +198,10 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         sched_ring[slot] = item;
         __threadfence_block();
         mbar_arrive(bar_sched_full0 + 8u * slot);
-        if (item >= sched.total_items) break;
+        if (item >= sched.total_items) {
+          griddep_launch_dependents();   // the queue is empty: the next kernel on the stream may set up
+          break;
+        }
         int bh, row0;
         decode(item, bh, row0);
         const int b = bh / p.H, h = bh - b * p.H;
@@ -208,6 +218,10 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           return true;
         };
         auto load_kv = [&](const CUtensorMap* map, int j) -> bool {
+          if (static_cast<int>(kv_count) == p.test_drop_load) {   // test hook: this tile is never announced
+            ++kv_count;
+            return true;
+          }
           const uint32_t s = kv_count % C::kStages;
           const uint32_t ph = (kv_count / C::kStages) & 1;
           if (!mbar_wait(bar_kv_empty(s), ph ^ 1, abort_flag, wait_ns, kTagKvEmpty)) return false;
@@ -607,7 +621,10 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   __syncthreads();
   tc_fence_after_sync();
   if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
-  if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
+  if (threadIdx.x == 0) {
+    if (*abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
+    queue_retire(p.tile_counter);
+  }
 }
 
 template <int D, bool kBf16>
@@ -627,11 +644,9 @@ cudaError_t launch_one(const FwdParams& p, int sm_count, cudaStream_t stream, lo
   static std::atomic<unsigned long long> smem_done{0};   // per kernel instantiation, bit per device
   cudaError_t e = set_dynamic_smem_once(smem_done, reinterpret_cast<const void*>(kern), C::kSmemBytes);
   if (e != cudaSuccess) return e;
-  e = cudaMemsetAsync(p.tile_counter, 0, sizeof(unsigned int), stream);
-  if (e != cudaSuccess) return e;
+  // No memset of the work queue: the last CTA of the launch that used it before put it back to zero.
   const int grid = sched.total_items < sm_count ? sched.total_items : sm_count;
-  kern<<<grid, kNumThreads, C::kSmemBytes, stream>>>(maps, p, sched);
-  e = cudaGetLastError();
+  e = launch_persistent(kern, grid, kNumThreads, C::kSmemBytes, stream, p.pdl != 0, maps, p, sched);
   if (e == cudaSuccess) *launches += 1;
   return e;
 }
@@ -717,8 +732,8 @@ cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t st
 namespace rsfa {
 namespace {
 
-// The whole scratch: word 0 = work-queue counter, word 1 = status word, rest unused.  Every GPU
-// that loads the library holds these 256 bytes until the process exits.
+// The whole scratch: words 0 and 1 = work queue (items handed out, CTAs finished), word 2 = status
+// word, rest unused.  Every GPU that loads the library holds these 256 bytes until the process exits.
 constexpr int kStaticScratchBytes = 256;
 static __device__ __align__(256) unsigned int g_static_scratch[kStaticScratchBytes / sizeof(unsigned int)];
 
@@ -763,6 +778,13 @@ int noalloc_setup(int device, NoAllocDevice** out) {
 }
 
 }  // namespace
+
+int* noalloc_status_word(int device) {
+  if (device < 0 || device >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  const NoAllocDevice& d = g_noalloc_dev[device];
+  return d.ready ? reinterpret_cast<int*>(d.scratch + 2) : nullptr;
+}
 }  // namespace rsfa
 
 extern "C" int rsfa_fwd_noalloc(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
@@ -823,9 +845,11 @@ extern "C" int rsfa_fwd_noalloc(const void* q, const void* k, const void* v, voi
     tcgen05_resolve_tile(S, D, causal, 0, 0, -1, &bm, &bn);   // no tile request here: the table decides
     p.tile_n = bn;
   }
-  p.tile_counter = d->scratch;      // cleared by the launcher on `stream` before the kernel
-  p.status = reinterpret_cast<int*>(d->scratch + 1);
-  p.wait_limit_ns = 2000ull * 1000000ull;
+  p.tile_counter = d->scratch;      // words 0 and 1, cleared on `stream` below
+  p.status = reinterpret_cast<int*>(d->scratch + 2);
+  p.wait_limit_ns = option_wait_limit_ns();
+  p.pdl = 0;                        // a memset precedes the kernel on the stream: nothing to overlap with
+  p.test_drop_load = option_test_drop_load();
   p.variant = -1;
   p.redo_count = nullptr;   // no scratch for the D = 64 separate-P kernel here: the 128-key kernel runs
   p.redo_flags = nullptr;
@@ -834,8 +858,9 @@ extern "C" int rsfa_fwd_noalloc(const void* q, const void* k, const void* v, voi
 #ifdef RSFA_TRACE
   p.trace = nullptr;
 #endif
-  // The status word keeps whatever the last call left; a fresh call starts from "ok".
-  if (cudaMemsetAsync(d->scratch + 1, 0, sizeof(unsigned int), static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+  // The block keeps whatever the last call left (a kernel puts its queue back to zero when it ends,
+  // but a call that was cut short may not have): a fresh call starts from zero queue words and "ok".
+  if (cudaMemsetAsync(d->scratch, 0, 3 * sizeof(unsigned int), static_cast<cudaStream_t>(stream)) != cudaSuccess) {
     cudaGetLastError();
     return RSFA_ERR_CUDA;
   }

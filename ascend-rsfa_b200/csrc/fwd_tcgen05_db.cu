@@ -153,6 +153,8 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
+  // Only this CTA's shared and tensor memory so far; global memory waits for the kernel in front.
+  griddep_wait();
 
   const int S = p.S;
   const int items_per_head = sched.items_per_head;
@@ -195,7 +197,10 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         sched_ring[slot] = item;
         __threadfence_block();
         mbar_arrive(bar_sched_full0 + 8u * slot);
-        if (item >= sched.total_items) break;
+        if (item >= sched.total_items) {
+          griddep_launch_dependents();   // the queue is empty: the next kernel on the stream may set up
+          break;
+        }
         int bh, row0;
         decode(item, bh, row0);
         const int b = bh / p.H, h = bh - b * p.H;
@@ -637,7 +642,10 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   __syncthreads();
   tc_fence_after_sync();
   if (warp == C::kMmaWarp0) tmem_dealloc(tmem_base, 512);
-  if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
+  if (threadIdx.x == 0) {
+    if (*abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
+    queue_retire(p.tile_counter);
+  }
 }
 
 template <int D, int NT, bool kBf16>
@@ -656,11 +664,9 @@ cudaError_t launch_db(const FwdParams& p, int sm_count, cudaStream_t stream, lon
   static std::atomic<unsigned long long> smem_done{0};   // per kernel instantiation, bit per device
   cudaError_t e = set_dynamic_smem_once(smem_done, reinterpret_cast<const void*>(kern), C::kSmemBytes);
   if (e != cudaSuccess) return e;
-  e = cudaMemsetAsync(p.tile_counter, 0, sizeof(unsigned int), stream);
-  if (e != cudaSuccess) return e;
+  // No memset of the work queue: the last CTA of the launch that used it before put it back to zero.
   const int grid = sched.total_items < sm_count ? sched.total_items : sm_count;
-  kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(maps, p, sched);
-  e = cudaGetLastError();
+  e = launch_persistent(kern, grid, C::kThreads, C::kSmemBytes, stream, p.pdl != 0, maps, p, sched);
   if (e == cudaSuccess) *launches += 1;
   return e;
 }

@@ -129,6 +129,8 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
+  // Only this CTA's shared and tensor memory so far; global memory waits for what is in front on the stream.
+  griddep_wait();
 
   const int S = p.S;
   const int items_per_head = sched.items_per_head;
@@ -170,7 +172,10 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           sched_ring[slot] = item;
           __threadfence_block();
           mbar_arrive(bar_sched_full0 + 8u * slot);
-          if (item >= sched.total_items) break;
+          if (item >= sched.total_items) {
+            griddep_launch_dependents();   // the queue is empty: the redo pass behind this kernel may set up
+            break;
+          }
           int bh, row0;
           decode(item, bh, row0);
           const int b = bh / p.H, h = bh - b * p.H;
@@ -484,7 +489,10 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   __syncthreads();
   tc_fence_after_sync();
   if (warp == kMmaWarpSp0) tmem_dealloc(tmem_base, 512);
-  if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
+  if (threadIdx.x == 0) {
+    if (*abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
+    queue_retire(p.tile_counter);
+  }
 }
 
 }  // namespace
@@ -508,14 +516,12 @@ static cudaError_t launch_sp_one(const FwdParams& p, int sm_count, cudaStream_t 
   static std::atomic<unsigned long long> smem_done{0};   // per kernel instantiation, bit per device
   cudaError_t e = set_dynamic_smem_once(smem_done, reinterpret_cast<const void*>(kern), kSmemBytesSp);
   if (e != cudaSuccess) return e;
-  e = cudaMemsetAsync(p.tile_counter, 0, sizeof(unsigned int), stream);
-  if (e != cudaSuccess) return e;
-  // the counter (padded to 4 words) and the flags are one block
+  // The redo counter (padded to 4 words) and the flags are one block, cleared for every call.  The work
+  // queue needs no memset: the last CTA of the launch that used it before put it back to zero.
   e = cudaMemsetAsync(p.redo_count, 0, (4 + static_cast<size_t>(sched.total_items)) * sizeof(int), stream);
   if (e != cudaSuccess) return e;
   const int grid = sched.total_items < sm_count ? sched.total_items : sm_count;
-  kern<<<grid, kThreadsSp, kSmemBytesSp, stream>>>(maps, p, sched);
-  e = cudaGetLastError();
+  e = launch_persistent(kern, grid, kThreadsSp, kSmemBytesSp, stream, false, maps, p, sched);
   if (e == cudaSuccess) *launches += 1;
   return e;
 }

@@ -15,10 +15,11 @@
 namespace {
 
 constexpr int kMaxDevices = 64;
-constexpr int kCounterSlots = 1024;  // one work-queue counter per launch in flight
-// Scratch of the D = 64 separate-P kernel: kRedoSlots blocks, used in turn by successive calls, each
-// [counter padded to 4 ints][kRedoCapacity flags][kRedoCapacity item ids].  Larger problems, and the
-// ninth call in flight on one device, are not the target: the former fall back to the 128-key kernel.
+constexpr int kCounterSlots = 1024;  // one work queue (two words) per launch in flight
+// Scratch of the D = 64 separate-P kernel: kRedoSlots blocks, each
+// [counter padded to 4 ints][kRedoCapacity flags][kRedoCapacity item ids].  A call takes a block whose
+// last user has finished on the GPU (an event per block says so); larger problems, and calls that
+// find every block still in use, run the 128-key kernel alone.
 constexpr int kRedoSlots = 8;
 constexpr int kRedoCapacity = 1 << 18;
 constexpr size_t kRedoBlockInts = 4 + 2 * static_cast<size_t>(kRedoCapacity);
@@ -27,10 +28,13 @@ struct DeviceState {
   bool ready = false;
   int sm_count = 0;
   int cc_major = 0;
-  unsigned int* counters = nullptr;  // kCounterSlots words
+  unsigned int* counters = nullptr;  // kCounterSlots work queues of two words (see FwdParams::tile_counter)
   int* status = nullptr;
+  int* status_mirror = nullptr;      // pinned host copy of the status word (the "check_status" option)
   unsigned next_slot = 0;
   int* redo = nullptr;               // kRedoSlots blocks, allocated at the first D = 64 call that can use them
+  cudaEvent_t redo_done[kRedoSlots] = {};   // recorded behind the last launches that used the block
+  bool redo_held[kRedoSlots] = {};          // a host thread is between taking the block and recording its event
   // staging buffers of rsfa_fwd_host (grow-only)
   void* stage[2][4] = {{nullptr, nullptr, nullptr, nullptr}, {nullptr, nullptr, nullptr, nullptr}};
   float* stage_lse[2] = {nullptr, nullptr};
@@ -46,6 +50,9 @@ std::atomic<long long> g_force_path{-1};
 std::atomic<long long> g_wait_limit_ms{2000};
 std::atomic<long long> g_host_slab_heads{0};
 std::atomic<long long> g_tcgen05_variant{-1};
+std::atomic<long long> g_pdl{1};
+std::atomic<long long> g_test_drop_load{-1};
+std::atomic<long long> g_check_status{0};
 #ifdef RSFA_TRACE
 std::atomic<long long> g_trace_ptr{0};
 #endif
@@ -64,9 +71,11 @@ int ensure_device(int device, DeviceState** out) {
     int prev = 0;
     if (cudaGetDevice(&prev) != cudaSuccess) return RSFA_ERR_CUDA;
     if (cudaSetDevice(device) != cudaSuccess) return RSFA_ERR_CUDA;
-    cudaError_t e = cudaMalloc(&d.counters, kCounterSlots * sizeof(unsigned int));
+    cudaError_t e = cudaMalloc(&d.counters, 2 * kCounterSlots * sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMalloc(&d.status, sizeof(int));
-    if (e == cudaSuccess) e = cudaMemset(d.counters, 0, kCounterSlots * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaHostAlloc(&d.status_mirror, sizeof(int), cudaHostAllocDefault);
+    if (e == cudaSuccess) *d.status_mirror = 0;
+    if (e == cudaSuccess) e = cudaMemset(d.counters, 0, 2 * kCounterSlots * sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMemset(d.status, 0, sizeof(int));
     cudaSetDevice(prev);
     if (e != cudaSuccess) {
@@ -116,6 +125,11 @@ void tile_of_path(int path, int S, int D, int causal, int req_bm, int req_bn, in
 
 namespace rsfa {
 void count_launches(long long n) { g_launches.fetch_add(n); }
+unsigned long long option_wait_limit_ns() {
+  return static_cast<unsigned long long>(g_wait_limit_ms.load()) * 1000000ull;
+}
+int option_pdl() { return static_cast<int>(g_pdl.load()); }
+int option_test_drop_load() { return static_cast<int>(g_test_drop_load.load()); }
 }  // namespace rsfa
 
 extern "C" {
@@ -165,6 +179,21 @@ int rsfa_set_option(const char* name, long long value) {
     g_host_slab_heads.store(value);
     return RSFA_OK;
   }
+  if (std::strcmp(name, "pdl") == 0) {
+    if (value < 0 || value > 1) return RSFA_ERR_INVALID_ARGUMENT;
+    g_pdl.store(value);
+    return RSFA_OK;
+  }
+  if (std::strcmp(name, "check_status") == 0) {
+    if (value < 0 || value > 1) return RSFA_ERR_INVALID_ARGUMENT;
+    g_check_status.store(value);
+    return RSFA_OK;
+  }
+  if (std::strcmp(name, "test_drop_load") == 0) {
+    if (value < -1 || value > 1000000) return RSFA_ERR_INVALID_ARGUMENT;
+    g_test_drop_load.store(value);
+    return RSFA_OK;
+  }
   return RSFA_ERR_INVALID_ARGUMENT;
 }
 
@@ -174,14 +203,26 @@ long long rsfa_get_option(const char* name) {
   if (std::strcmp(name, "wait_limit_ms") == 0) return g_wait_limit_ms.load();
   if (std::strcmp(name, "host_slab_heads") == 0) return g_host_slab_heads.load();
   if (std::strcmp(name, "tcgen05_variant") == 0) return g_tcgen05_variant.load();
+  if (std::strcmp(name, "pdl") == 0) return g_pdl.load();
+  if (std::strcmp(name, "check_status") == 0) return g_check_status.load();
+  if (std::strcmp(name, "test_drop_load") == 0) return g_test_drop_load.load();
+  if (std::strcmp(name, "workspace_devices") == 0) {   // read-only: devices on which rsfa_fwd has made its workspace
+    std::lock_guard<std::mutex> lock(g_mu);
+    long long n = 0;
+    for (int i = 0; i < kMaxDevices; ++i) n += g_dev[i].ready ? 1 : 0;
+    return n;
+  }
   return RSFA_ERR_INVALID_ARGUMENT;
 }
 
 int rsfa_sm_count(int device) {
-  DeviceState* d = nullptr;
-  const int rc = ensure_device(device, &d);
-  if (rc != RSFA_OK) return rc;
-  return d->sm_count;
+  int major = 0, sms = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+    cudaGetLastError();
+    return RSFA_ERR_NO_DEVICE;
+  }
+  return major == 10 ? sms : RSFA_ERR_NO_DEVICE;   // the kernels are built for sm_100a only
 }
 
 int rsfa_select_path(int S, int D, int causal, float sm_scale, int block_m, int block_n, int dtype,
@@ -207,19 +248,55 @@ int rsfa_get_tiling(int B, int H, int S, int D, int causal, int* block_m, int* b
   return RSFA_OK;
 }
 
+int rsfa_work_items(int B, int H, int S, int D, int causal, float sm_scale, long long* items) {
+  if (items == nullptr || B < 1 || H < 1 || S < 1 || !valid_head_dim(D)) return RSFA_ERR_INVALID_ARGUMENT;
+  const long long heads = static_cast<long long>(B) * H;
+  if (choose_path(S, D, sm_scale, heads) == RSFA_PATH_GENERIC) {
+    *items = rsfa::generic_grid_blocks(B, H, S);
+  } else {
+    const int rows = (D == 256) ? 128 : 256;   // query rows per work item of the tcgen05 kernels
+    *items = heads * ((S + rows - 1) / rows);
+  }
+  (void)causal;   // masked row blocks are still work items (lighter ones)
+  return RSFA_OK;
+}
+
 int rsfa_device_status(int device, int* raw) {
+  if (device < 0 || device >= kMaxDevices) return RSFA_ERR_INVALID_ARGUMENT;
+  // Looks only at what exists: the workspace of rsfa_fwd if a call has created it, the static block
+  // of rsfa_fwd_noalloc if that has been used.  It allocates nothing itself.
   DeviceState* d = nullptr;
-  int rc = ensure_device(device, &d);
-  if (rc != RSFA_OK) return rc;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (g_dev[device].ready) d = &g_dev[device];
+  }
+  int* na = rsfa::noalloc_status_word(device);
   int prev = 0;
   cudaGetDevice(&prev);
-  if (cudaSetDevice(device) != cudaSuccess) return RSFA_ERR_CUDA;
+  if (cudaSetDevice(device) != cudaSuccess) {
+    cudaGetLastError();
+    return RSFA_ERR_NO_DEVICE;
+  }
   int word = 0;
   cudaError_t e = cudaDeviceSynchronize();
-  if (e == cudaSuccess) e = cudaMemcpy(&word, d->status, sizeof(int), cudaMemcpyDeviceToHost);
-  if (e == cudaSuccess && word != 0) e = cudaMemset(d->status, 0, sizeof(int));
+  if (e == cudaSuccess && d != nullptr) {
+    e = cudaMemcpy(&word, d->status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && word != 0) e = cudaMemset(d->status, 0, sizeof(int));
+    *d->status_mirror = 0;
+  }
+  if (e == cudaSuccess && na != nullptr) {
+    int word_na = 0;
+    e = cudaMemcpy(&word_na, na, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && word_na != 0) {
+      e = cudaMemset(na, 0, sizeof(int));
+      if (word == 0) word = word_na;
+    }
+  }
   cudaSetDevice(prev);
-  if (e != cudaSuccess) return RSFA_ERR_CUDA;
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return RSFA_ERR_CUDA;
+  }
   if (raw != nullptr) *raw = word;
   return word == 0 ? RSFA_OK : RSFA_ERR_DEVICE_STATUS;
 }
@@ -274,11 +351,19 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   p.sm_scale = sm_scale;
   p.bf16 = (dtype == RSFA_DTYPE_BF16) ? 1 : 0;
   p.status = d->status;
+  const bool check_status = g_check_status.load() != 0;
+  if (check_status && *static_cast<volatile int*>(d->status_mirror) != 0) {
+    // A kernel of an earlier call left a non-zero status word and its copy has reached the host:
+    // this call is not launched; rsfa_device_status() reports the word and clears it.
+    return RSFA_ERR_DEVICE_STATUS;
+  }
   {
     std::lock_guard<std::mutex> lock(g_mu);
-    p.tile_counter = d->counters + (d->next_slot++ % kCounterSlots);
+    p.tile_counter = d->counters + 2 * (d->next_slot++ % kCounterSlots);
   }
-  p.wait_limit_ns = static_cast<unsigned long long>(g_wait_limit_ms.load()) * 1000000ull;
+  p.wait_limit_ns = rsfa::option_wait_limit_ns();
+  p.pdl = rsfa::option_pdl();
+  p.test_drop_load = rsfa::option_test_drop_load();
 #ifdef RSFA_TRACE
   p.trace = reinterpret_cast<unsigned long long*>(g_trace_ptr.load());
 #endif
@@ -290,6 +375,7 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
 
   long long launches = 0;
   cudaError_t e;
+  int redo_slot = -1;
   const int path = choose_path(S, D, sm_scale, static_cast<long long>(B) * H);
   {
     int bm = 0, bn = 0;
@@ -309,12 +395,27 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
       }
       cudaSetDevice(prev);
     }
-    if (d->redo != nullptr) {
-      int* block = d->redo + (d->next_slot % kRedoSlots) * kRedoBlockInts;
+    // A block that no host thread holds and whose last user has finished on the GPU.  None free
+    // (eight such calls still in flight on this device): this call runs the 128-key kernel alone,
+    // which needs no scratch.
+    for (int i = 0; d->redo != nullptr && i < kRedoSlots && redo_slot < 0; ++i) {
+      if (d->redo_held[i]) continue;
+      if (d->redo_done[i] == nullptr &&
+          cudaEventCreateWithFlags(&d->redo_done[i], cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        d->redo_done[i] = nullptr;
+        continue;
+      }
+      if (cudaEventQuery(d->redo_done[i]) == cudaSuccess) redo_slot = i;
+      else cudaGetLastError();
+    }
+    if (redo_slot >= 0) {
+      int* block = d->redo + redo_slot * kRedoBlockInts;
       p.redo_count = block;
       p.redo_flags = block + 4;
       p.redo_list = block + 4 + kRedoCapacity;
       p.redo_capacity = kRedoCapacity;
+      d->redo_held[redo_slot] = true;   // until the event is recorded behind this call's launches
     }
   }
   if (path == RSFA_PATH_TCGEN05)
@@ -322,6 +423,17 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   else
     e = rsfa::launch_fwd_generic(p, static_cast<cudaStream_t>(stream), &launches);
   g_launches.fetch_add(launches);
+  if (redo_slot >= 0) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (cudaEventRecord(d->redo_done[redo_slot], static_cast<cudaStream_t>(stream)) != cudaSuccess) cudaGetLastError();
+    d->redo_held[redo_slot] = false;
+  }
+  if (e == cudaSuccess && check_status) {
+    // The status word follows the kernels to the host on the same stream; the next call looks at it.
+    if (cudaMemcpyAsync(d->status_mirror, d->status, sizeof(int), cudaMemcpyDeviceToHost,
+                        static_cast<cudaStream_t>(stream)) != cudaSuccess)
+      cudaGetLastError();
+  }
   if (e != cudaSuccess) {
     cudaGetLastError();
     return RSFA_ERR_CUDA;

@@ -32,8 +32,8 @@ constexpr float kSumLimit = RSFA_SUM_LIMIT;
 
 // Wait-site tags (reported in the status word when a wait runs out).
 enum : int {
-  kTagQEmpty = 1, kTagKvEmpty, kTagQFull, kTagKvFull, kTagPFull, kTagSFull, kTagOFull, kTagSched, kTagEpilogue,
-  kTagPvDone
+  kTagQEmpty = 1, kTagKvEmpty = 2, kTagQFull = 3, kTagKvFull = 4, kTagPFull = 5, kTagSFull = 6, kTagOFull = 7,
+  kTagSched = 8, kTagPvDone = 10
 };
 
 // Debug builds (-DRSFA_TRACE) log (clock, code) pairs per role for CTA 0; the product build
@@ -257,22 +257,58 @@ __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
 }
 
+// Last act of a CTA of a persistent kernel (one thread, after the CTA's final barrier): count the CTA as
+// finished in word [1] of the work queue; the CTA that completes the count puts both words back
+// to zero.  Every CTA's own additions to word [0] are behind it by then, so the pair is zero again
+// when the grid has exited - also when the CTAs left early through the wait-expired path.
+__device__ __forceinline__ void queue_retire(unsigned int* queue) {
+  __threadfence();
+  if (atomicAdd(queue + 1, 1u) == gridDim.x - 1) {
+    queue[0] = 0u;
+    queue[1] = 0u;
+    __threadfence();
+  }
+}
+
 // ---------------------------------------------------------------- host side
+// Launch of a persistent kernel, with programmatic stream serialisation when `pdl` is set: the
+// kernel may then begin its set-up (barriers, tensor-memory allocation, descriptor prefetch) while
+// the kernel in front of it on the stream drains, and waits in griddep_wait() before it touches
+// global memory.
+template <typename Kernel, typename... Args>
+cudaError_t launch_persistent(Kernel kern, int grid, int threads, size_t smem, cudaStream_t stream, bool pdl,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned int>(grid));
+  cfg.blockDim = dim3(static_cast<unsigned int>(threads));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                   CUtensorMapFloatOOBfill);
 
 EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
+  static std::atomic<EncodeTiledFn> fn{nullptr};
+  EncodeTiledFn f = fn.load(std::memory_order_acquire);
+  if (f == nullptr) {
     void* ptr = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+        qres == cudaDriverEntryPointSuccess) {
+      f = reinterpret_cast<EncodeTiledFn>(ptr);
+      fn.store(f, std::memory_order_release);
+    }
   }
-  return fn;
+  return f;
 }
 
 // [B,H,S,D] tensor, 16-bit elements, as a 4-D map (D, S, H, B) with boxes of 64 x `box_rows`.
@@ -281,12 +317,13 @@ bool make_map(CUtensorMap* map, const void* base, const FwdParams& p, const int6
   if (enc == nullptr) return false;
   const cuuint64_t dims[4] = {static_cast<cuuint64_t>(p.D), static_cast<cuuint64_t>(p.S),
                               static_cast<cuuint64_t>(p.H), static_cast<cuuint64_t>(p.B)};
-  // A dimension of extent 1 may carry any stride; keep the encoder happy with a legal one.
-  auto stride_bytes = [&](int64_t s, int64_t fallback) {
-    return static_cast<cuuint64_t>((s > 0 ? s : fallback) * 2);
+  // A dimension of extent 1 may carry any stride (PyTorch leaves whatever the view had): the
+  // encoder wants multiples of 16 bytes, so such a dimension gets the dense stride instead.
+  auto stride_bytes = [&](int64_t s, int extent, int64_t dense) {
+    return static_cast<cuuint64_t>(((extent > 1 && s > 0) ? s : dense) * 2);
   };
-  const cuuint64_t strides[3] = {stride_bytes(st[2], p.D), stride_bytes(st[1], static_cast<int64_t>(p.S) * p.D),
-                                 stride_bytes(st[0], static_cast<int64_t>(p.H) * p.S * p.D)};
+  const cuuint64_t strides[3] = {stride_bytes(st[2], p.S, p.D), stride_bytes(st[1], p.H, static_cast<int64_t>(p.S) * p.D),
+                                 stride_bytes(st[0], p.B, static_cast<int64_t>(p.H) * p.S * p.D)};
   const cuuint32_t box[4] = {64u, static_cast<cuuint32_t>(box_rows), 1u, 1u};
   const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
   const CUresult r = enc(map, p.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,

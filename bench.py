@@ -2,24 +2,35 @@
 """Benchmark of the FlashAttention-2 forward hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--config cfg2] [--causal 0|1] [--e2e-steps E]
+                    [--config cfg2] [--causal 0|1] [--e2e-steps E] [--no-extras]
 
 One "step" is one forward pass of `attention()` over the whole configured batch
-(default: benchmark configuration cfg2 — B=128, H=8, S=2048, D=128, fp16, sm_scale=0.5,
+(default: benchmark configuration cfg2 - B=128, H=8, S=2048, D=128, fp16, sm_scale=0.5,
 non-causal; the causal pass of the same shape is timed separately and reported
-under "causal").  For N > 1 the script is launched with torchrun, one rank per
+under "other_mask").  For N > 1 the script is launched with torchrun, one rank per
 GPU; the B*H heads of the SAME problem are split across ranks (no collective in
 the timed region) and the value is total FLOPs / slowest rank's time.
 
-Prints ONE JSON line on rank 0.  `value` is device-resident throughput (inputs
-already in HBM), `e2e` is the same metric through `attention_host()` with pinned
-host tensors (host->device and device->host copies inside the timed region),
-`roofline` relates the kernel to the measured tensor-core peak, `cpu_baseline`
-is the fp32 reference math on the host cores for a bounded sample.
+Prints ONE JSON line on rank 0.  Keys beyond the basic contract:
+
+  value / roofline   device-resident throughput of the K timed steps (inputs already in HBM) against the
+                     measured tensor-core peak; a run of 20 steps lasts 35 ms, i.e. it is a burst at full clock
+  sustained          the same launch repeated for 3 s with one event pair per launch: median of the last
+                     third, the SM clock sampled over that window, and the fraction of the sustained peak
+  parity             >= 8 heads spread over every rank's slab (first and last included) of the output of a
+                     full launch, against the fp32 oracle on the CPU, AND-ed over ranks; at N > 1 also an
+                     NCCL all-gather of the output slabs (outside every timed region) whose per-slab
+                     checksums must equal the ones each rank computed locally
+  configs            the other benchmark configurations (cfg3, cfg4, cfg5), both masks, 20 steps each
+  short_seq          (N = 1) the HBM-bound short-sequence shapes as bytes / time against the measured copy rate
+  launch_floor_us    (N = 1) what one launch costs beyond its work items: t(1 wave) - (t(2 waves) - t(1 wave))
+  e2e                the same metric through `attention_host()` with pinned host tensors (host->device and
+                     device->host copies inside the timed region), with the plain-copy floor of the box beside it
+  cpu_baseline       (N = 1) the fp32 reference math on the host cores for a bounded sample
 
 `--impl reference` times the reference math (softmax(QK^T*s)V in fp32 through
-PyTorch on the host cores — the reference project has no CPU or CUDA
-implementation of its own to run here) on a bounded sample of the same config.
+PyTorch on the host cores - the reference project has no CPU or CUDA
+implementation of its own to run here) on the WHOLE configuration per step.
 """
 import argparse
 import json
@@ -35,24 +46,30 @@ sys.path.insert(0, os.path.join(ROOT, "ascend-rsfa_b200"))
 import torch
 
 METRIC = "attention fwd TFLOP/s (whole job; causal FLOPs counted as half)"
-# DRAM bytes (read + write) per (batch, head) of S=2048, D=128: dram__bytes_read.sum + dram__bytes_write.sum
-# of one ncu capture of this kernel on 128 heads of the shape (201.4 + 48.0 MB); traffic is proportional
-# to the number of heads (Q, K, V read once, O written once; the re-reads of K/V are served by L2).
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the 128-key tcgen05 kernel per
+# (batch, head) of S=2048, D=128, from the ncu capture summarised in the file below (128 heads of the shape:
+# 201.4 MB read + 48.0 MB written); traffic is proportional to the number of heads (Q, K, V read once, O
+# written once; the re-reads of K/V are served by L2).
 NCU_DRAM_BYTES_PER_HEAD_S2048_D128 = 249.4e6 / 128
-FALLBACK_PEAK_TFLOPS = 1590.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
+NCU_TRAFFIC_SOURCE = "profiles/fwd_tcgen05_d128_s2048_ncu_full.md"
+# Peaks used only when MEASURED_PEAKS.json is absent: cuBLAS bf16 burst / sustained TFLOP/s and copy GB/s.
+FALLBACK_PEAKS = {"burst": 1590.0, "sustained": 1400.0, "hbm_gbs": 6650.0}
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="cfg2")
     ap.add_argument("--causal", type=int, default=0)
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--sustained-seconds", type=float, default=3.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="leave out the sustained, configs, short_seq and launch_floor records (profiler captures)")
     ap.add_argument("--batch", type=int, default=0,
                     help="override the config's batch size (small cases for profiler captures; the default "
                          "run and every reported number use the config's own)")
@@ -67,7 +84,7 @@ def load_peaks():
         return {"burst": float(d["bf16_tflops"]), "sustained": float(d.get("bf16_tflops_sustained", 0.0)),
                 "hbm_gbs": float(d.get("hbm_gbs", 0.0)), "source": "measured"}
     except Exception:
-        return {"burst": FALLBACK_PEAK_TFLOPS, "sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+        return dict(FALLBACK_PEAKS, source="fallback")
 
 
 class ClockSampler:
@@ -77,7 +94,7 @@ class ClockSampler:
     NOTE = {"sw_power_cap": 0x4}
 
     def __init__(self, index):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.samples, self.times, self.reasons, self.max_mhz = [], [], set(), None
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -94,6 +111,7 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                self.times.append(time.perf_counter())
                 mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
                 for name, bit in list(self.BAD.items()) + list(self.NOTE.items()):
                     if mask & bit:
@@ -113,6 +131,10 @@ class ClockSampler:
         if self._thread is not None:
             self._thread.join()
 
+    def median_since(self, t0):
+        s = sorted(m for m, t in zip(self.samples, self.times) if t >= t0)
+        return s[len(s) // 2] if s else None
+
     def summary(self):
         s = sorted(self.samples)
         return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
@@ -129,8 +151,22 @@ def physical_gpu_index(local_rank):
     return local_rank
 
 
-def cpu_reference_sample(cfg, causal, target_seconds, repeats=1):
-    """Time the fp32 reference math on all host cores over `n` whole heads of the config."""
+def workload_name(name, cfg, causal):
+    B, H, S, D, scale, mult = cfg
+    return "%s %s: B=%d H=%d S=%d D=%d sm_scale=%g%s" % (name, "causal" if causal else "non-causal", B, H, S, D,
+                                                         scale, "" if mult == 1.0 else " inputs x%g" % mult)
+
+
+def config_record(name, cfg, causal):
+    """The `config` object, the same for both arms."""
+    B, H, S, D, _, _ = cfg
+    mib = 4.0 * B * H * S * D * 2 / 2 ** 20
+    return {"workload": workload_name(name, cfg, causal), "inputs": "fp16 i.i.d. N(0,1) from a seed, [B,H,S,D] contiguous",
+            "l2": "inputs+outputs %.0f MiB per step, %s the 126 MB L2" % (mib, "larger than" if mib > 126 else "NOT larger than")}
+
+
+def cpu_reference_sample(cfg, causal, target_seconds):
+    """Time the fp32 reference math on all host cores over whole heads of the config."""
     from oracle.attention_ref import attention_flops, attention_fp32, make_inputs
     B, H, S, D, scale, mult = cfg
     cores = os.cpu_count() or 1
@@ -157,6 +193,7 @@ def cpu_reference_sample(cfg, causal, target_seconds, repeats=1):
 
 
 def run_reference(args, cfg_name, cfg):
+    """The reference arm: the fp32 reference math on the host cores, the WHOLE configuration per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -165,32 +202,51 @@ def run_reference(args, cfg_name, cfg):
     from oracle.attention_ref import attention_flops, attention_fp32, make_inputs
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    n = 8  # heads per step: a bounded sample of the same workload
-    q, k, v = make_inputs(1, n, S, D, seed=42, std=mult)
-    for _ in range(max(1, min(args.warmup, 2))):
-        attention_fp32(q, k, v, causal, scale)
-    steps = max(1, min(args.steps, 10))
+    heads = B * H
+    chunk = min(heads, 128)                      # generated once, reused for every chunk of the step
+    q, k, v = make_inputs(1, chunk, S, D, seed=42, std=mult)
+
+    def step():
+        done = 0
+        while done < heads:
+            n = min(chunk, heads - done)
+            attention_fp32(q[:, :n], k[:, :n], v[:, :n], causal, scale)
+            done += n
+
+    t0 = time.perf_counter()
+    step()                                       # warm-up, also tells how long a step takes
+    t_step = time.perf_counter() - t0
+    warmup = 1
+    # as many of the requested steps as fit in about three minutes of host time
+    steps = int(max(1, min(args.steps, 180.0 / max(t_step, 1e-3))))
     t0 = time.perf_counter()
     for _ in range(steps):
-        attention_fp32(q, k, v, causal, scale)
+        step()
     dt = (time.perf_counter() - t0) / steps
-    val = attention_flops(1, n, S, D, causal) / dt / 1e12
-    sample = "%d of %d (batch,head) pairs per step, fp32 PyTorch on %d host threads" % (n, B * H, cores)
+    val = attention_flops(B, H, S, D, causal) / dt / 1e12
+    sample = ("all %d (batch,head) pairs per step (inputs of %d heads reused), fp32 PyTorch on %d host threads; "
+              "%d of the %d requested steps, %d warm-up" % (heads, chunk, cores, steps, args.steps, warmup))
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "%s %s B=%d H=%d S=%d D=%d" % (cfg_name, "causal" if causal else "non-causal", B, H, S, D),
-                   "sample": sample},
+        "config": config_record(cfg_name, cfg, causal),
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
+def spread(n, k):
+    """k indices spread over range(n), first and last included."""
+    if n <= k:
+        return list(range(n))
+    return sorted({int(round(i * (n - 1) / (k - 1))) for i in range(k)})
+
+
 def main():
     args = parse_args()
-    from oracle.attention_ref import CONFIGS, attention_flops
+    from oracle.attention_ref import CONFIGS, attention_flops, attention_fp32, error_metrics
     cfg = CONFIGS[args.config]
     if args.impl == "reference":
         run_reference(args, args.config, cfg)
@@ -209,31 +265,39 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-
-    B, H, S, D, scale, mult = cfg
-    if args.batch > 0:
-        B = args.batch
-        cfg = (B, H, S, D, scale, mult)
-    heads = B * H
-    lo, hi = sharding.head_slab(heads, rank, world)
-    n_local = hi - lo
-    bm, bn = fa.get_tiling(B, H, S, D, bool(args.causal))
-
-    # This rank's slab of the seeded problem, generated on the device (inputs resident in HBM).
-    g = torch.Generator(device=dev).manual_seed(42 + rank)
-    def mk():
-        t = torch.randn((1, n_local, S, D), generator=g, device=dev, dtype=torch.float32)
-        if mult != 1.0:
-            t.mul_(mult)
-        return t.to(torch.float16)
-    q, k, v = mk(), mk(), mk()
+    peaks = load_peaks()
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(causal, steps, warmup):
+    def reduce_max(x):
+        if dist is None:
+            return float(x)
+        t = torch.tensor([float(x)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def reduce_min(x):
+        return -reduce_max(-float(x))
+
+    def make_slab(c, seed):
+        """This rank's slab of the seeded problem `c`, generated on the device (inputs resident in HBM)."""
+        B, H, S, D, _, mult = c
+        lo, hi = sharding.head_slab(B * H, rank, world)
+        g = torch.Generator(device=dev).manual_seed(seed + rank)
+
+        def mk():
+            t = torch.randn((1, hi - lo, S, D), generator=g, device=dev, dtype=torch.float32)
+            if mult != 1.0:
+                t.mul_(mult)
+            return t.to(torch.float16)
+        return mk(), mk(), mk()
+
+    def timed(c, tensors, causal, steps, warmup):
+        B, H, S, D, scale, _ = c
+        q, k, v = tensors
         bm, bn = fa.get_tiling(B, H, S, D, causal)   # the table's tile for this mask
         for _ in range(warmup):
             fa.attention(q, k, v, causal, scale, bm, bn)
@@ -245,29 +309,184 @@ def main():
             fa.attention(q, k, v, causal, scale, bm, bn)
         ev1.record()
         barrier()
-        ms = ev0.elapsed_time(ev1) / steps
-        launches = fa.launch_count() - launches0
-        if dist is not None:
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms, launches
+        ms = reduce_max(ev0.elapsed_time(ev1) / steps)
+        return ms, fa.launch_count() - launches0, (bm, bn)
 
+    def parity(c, tensors, causal, n_heads):
+        """Heads spread over this rank's slab (first and last included) of the output of ONE full launch
+        against the fp32 oracle on the CPU; AND / MAX over all ranks."""
+        B, H, S, D, scale, _ = c
+        q, k, v = tensors
+        bm, bn = fa.get_tiling(B, H, S, D, causal)
+        o = fa.attention(q, k, v, causal, scale, bm, bn)
+        torch.cuda.synchronize()
+        idx = spread(q.shape[1], n_heads)
+        sel = torch.tensor(idx, device=dev)
+        ref = attention_fp32(q[:, sel].cpu(), k[:, sel].cpu(), v[:, sel].cpu(), causal, scale)
+        m = error_metrics(o[:, sel], ref)
+        ok = reduce_min(1.0 if (m["finite"] and m["allclose"]) else 0.0) > 0.5
+        return {"ok": ok, "heads": len(idx), "ranks": world, "max_abs": reduce_max(m["max_abs"]),
+                "atol": 1e-2, "rtol": 1e-2, "head_index_in_slab": idx if rank == 0 else None}, o
+
+    # ------------------------------------------------------------------ headline: value, other mask, parity
+    B, H, S, D, scale, mult = cfg
+    if args.batch > 0:
+        B = args.batch
+        cfg = (B, H, S, D, scale, mult)
+    heads = B * H
     main_causal = bool(args.causal)
+    slab = make_slab(cfg, 42)
+    q, k, v = slab
+    n_local = q.shape[1]
+    warmup = max(3, args.warmup)
     with ClockSampler(physical_gpu_index(local_rank)) as clocks:
-        ms, launches = timed(main_causal, args.steps, max(3, args.warmup))
+        ms, launches, (bm, bn) = timed(cfg, slab, main_causal, args.steps, warmup)
     fa.device_status()
     flops = attention_flops(B, H, S, D, main_causal)
     value = flops / (ms * 1e-3) / 1e12
-    other_ms, _ = timed(not main_causal, max(5, args.steps // 2), 3)
+    other_ms, _, _ = timed(cfg, slab, not main_causal, max(5, args.steps // 2), 3)
     other_val = attention_flops(B, H, S, D, not main_causal) / (other_ms * 1e-3) / 1e12
+    par, o_local = parity(cfg, slab, main_causal, 8)
+    par_other, _ = parity(cfg, slab, not main_causal, 8)
+    par["other_mask"] = {"ok": par_other["ok"], "heads": par_other["heads"], "max_abs": par_other["max_abs"]}
 
-    # sanity: one head against the fp32 oracle (outside every timed region)
-    from oracle.attention_ref import attention_fp32, error_metrics
-    o = fa.attention(q[:, :1], k[:, :1], v[:, :1], main_causal, scale, bm, bn)
-    err = error_metrics(o, attention_fp32(q[:, :1].cpu(), k[:, :1].cpu(), v[:, :1].cpu(), main_causal, scale))
+    # N > 1: the one allowed use of NCCL - gather the output slabs (outside every timed region) and check
+    # that every slab of the assembled tensor has the checksums its owner computed locally
+    if dist is not None:
+        t0 = time.perf_counter()
+        gathered = sharding.gather_heads(o_local, heads)
+        torch.cuda.synchronize()
+        gather_s = time.perf_counter() - t0
+        def checksums(x):
+            # exact and independent of the order of summation: the fp16 bit patterns as integers, plain and
+            # weighted by position (mod 2^64)
+            bits = x.contiguous().view(torch.int16).reshape(-1).long()
+            w = torch.arange(bits.numel(), device=x.device, dtype=torch.int64) % 8191 + 1
+            return torch.stack([bits.sum(), (bits * w).sum()])
+        mine = checksums(o_local)
+        sums = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(sums, mine)
+        ok = gathered.shape[1] == heads
+        for r in range(world):
+            lo_r, hi_r = sharding.head_slab(heads, r, world)
+            ok = ok and bool(torch.equal(checksums(gathered[:, lo_r:hi_r]), sums[r]))
+        par["gather"] = {"ok": reduce_min(1.0 if ok else 0.0) > 0.5, "collective": "ncclAllGather of the O slabs",
+                         "bytes": int(gathered.numel() * 2), "seconds": gather_s, "in_timed_region": False}
+        par["ok"] = par["ok"] and par["gather"]["ok"]
+        del gathered
+    del o_local
 
-    # end to end: pinned host tensors in, host tensor out, copies inside the timed region
+    extras = not args.no_extras
+    sustained = None
+    # ------------------------------------------------------------------ launch floor (N = 1)
+    launch_floor = None
+    if extras and world == 1:
+        sms = fa.get_num_compute_cores()
+        lf_cfg = lambda nh: (1, nh, 1024, 128, 0.5, 1.0)     # 4 work items of 256 rows per head
+        h1 = max(1, sms // 4)
+        t = {}
+        for waves in (1, 2):
+            c = lf_cfg(h1 * waves)
+            t[waves], _, _ = timed(c, make_slab(c, 7), False, 200, 20)
+        launch_floor = {"us": (2 * t[1] - t[2]) * 1e3, "t_one_wave_us": t[1] * 1e3, "t_two_waves_us": t[2] * 1e3,
+                        "shape": "S=1024 D=128 non-causal, %d and %d heads = 1 and 2 work items per SM, 200 "
+                                 "back-to-back launches each" % (h1, 2 * h1)}
+
+    # ------------------------------------------------------------------ the other benchmark configurations
+    configs = None
+    if extras and args.batch == 0:
+        configs = {}
+        for name in ("cfg3", "cfg4", "cfg5"):
+            if name == args.config:
+                continue
+            c = CONFIGS[name]
+            cB, cH, cS, cD, cscale, _ = c
+            if cB * cH < world:
+                continue
+            tensors = make_slab(c, 42)
+            rec = {"workload": workload_name(name, c, False).replace(" non-causal", "")}
+            for causal in (False, True):
+                c_ms, _, tile = timed(c, tensors, causal, 20, 3)
+                tf = attention_flops(cB, cH, cS, cD, causal) / (c_ms * 1e-3) / 1e12
+                p_rec, _ = parity(c, tensors, causal, 8 if world == 1 else 2)
+                rec["causal" if causal else "non_causal"] = {
+                    "tflops": tf, "ms_per_step": c_ms, "frac_of_measured_burst": tf / world / peaks["burst"],
+                    "tile": list(tile), "steps": 20,
+                    "parity": {"ok": p_rec["ok"], "heads": p_rec["heads"], "ranks": world, "max_abs": p_rec["max_abs"]}}
+            configs[name] = rec
+            del tensors
+        fa.device_status()
+
+    # ------------------------------------------------------------------ short sequences: HBM-bound (N = 1)
+    short_seq = None
+    if extras and world == 1 and args.batch == 0:
+        short_seq = []
+        for (sB, sH, sS, sD, sscale, bmn) in ((1, 2, 128, 64, 0.5, (64, 64)), (4, 32, 64, 64, 0.5, (64, 64)),
+                                               (4, 32, 128, 128, 0.5, (64, 64)), (512, 8, 128, 128, 0.5, (128, 128))):
+            nbytes = 4 * sB * sH * sS * sD * 2
+            # input sets rotated through a pool of at least 300 MB (the L2 holds 126 MB)
+            sets = int(max(2, min(8192, (300 << 20) // (3 * nbytes // 4) + 1)))
+            g = torch.Generator(device=dev).manual_seed(5)
+            pool = torch.randn((sets, 3, sB, sH, sS, sD), generator=g, device=dev, dtype=torch.float16)
+            views = [(pool[i, 0], pool[i, 1], pool[i, 2]) for i in range(sets)]
+            n_it = 400
+            for causal in (False,):
+                for i in range(10):
+                    fa.attention(*views[i % sets], causal, sscale, *bmn)
+                torch.cuda.synchronize()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
+                for i in range(n_it):
+                    fa.attention(*views[i % sets], causal, sscale, *bmn)
+                ev1.record()
+                torch.cuda.synchronize()
+                us = ev0.elapsed_time(ev1) / n_it * 1e3
+                # the tcgen05 kernels take 256 query rows per work item, the short-sequence kernel 64
+                path = 1 if (sS > 64 and fa.work_items(sB, sH, sS, sD, causal, sscale) == sB * sH) else 0
+                o = fa.attention(pool[0, 0], pool[0, 1], pool[0, 2], causal, sscale, *bmn)
+                torch.cuda.synchronize()
+                sel = spread(sB * sH, 8)
+                flat = lambda x: x.reshape(1, sB * sH, sS, sD)[:, sel]
+                m = error_metrics(flat(o), attention_fp32(flat(pool[0, 0]).cpu(), flat(pool[0, 1]).cpu(),
+                                                          flat(pool[0, 2]).cpu(), causal, sscale))
+                short_seq.append({"shape": [sB, sH, sS, sD], "causal": causal, "us_per_call": us,
+                                  "bytes_per_call": nbytes, "gb_per_s": nbytes / (us * 1e-6) / 1e9,
+                                  "frac_of_measured_hbm": nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
+                                  "kernel": "tcgen05 (one key tile per work item)" if path == 1 else "short-sequence (mma.sync)",
+                                  "input_sets_rotated": sets,
+                                  "parity": {"ok": bool(m["finite"] and m["allclose"]), "heads": len(sel),
+                                             "max_abs": m["max_abs"]}})
+            del pool, views
+        fa.device_status()
+
+    # ------------------------------------------------------------------ sustained clock regime (N = 1)
+    if extras and world == 1:
+        n_launch = int(max(60, min(6000, args.sustained_seconds / (ms * 1e-3))))
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_launch + 1)]
+        with ClockSampler(physical_gpu_index(local_rank)) as cs:
+            torch.cuda.synchronize()
+            t_start = time.perf_counter()
+            evs[0].record()
+            for i in range(n_launch):
+                fa.attention(q, k, v, main_causal, scale, bm, bn)
+                evs[i + 1].record()
+            torch.cuda.synchronize()
+            t_end = time.perf_counter()
+        per = [evs[i].elapsed_time(evs[i + 1]) for i in range(n_launch)]
+        last = sorted(per[-(n_launch // 3):])
+        s_ms = last[len(last) // 2]
+        s_mhz = cs.median_since(t_start + (t_end - t_start) * 2.0 / 3.0)
+        s_tf = flops / (s_ms * 1e-3) / 1e12
+        b_mhz = clocks.summary()["sm_mhz"]
+        sustained = {"launches": n_launch, "seconds": t_end - t_start, "ms_per_step": s_ms, "sm_mhz": s_mhz,
+                     "tflops": s_tf, "peak": peaks["sustained"],
+                     "frac": (s_tf / peaks["sustained"]) if peaks["sustained"] else None,
+                     "reasons": sorted(cs.reasons),
+                     "ms_x_mhz": {"burst": (ms * b_mhz) if b_mhz else None, "sustained": (s_ms * s_mhz) if s_mhz else None},
+                     "note": "median of the last third of back-to-back launches, one CUDA event pair per launch"}
+        del evs
+
+    # ------------------------------------------------------------------ end to end: host tensors in and out
     e2e = None
     if not args.no_e2e:
         qh, kh, vh = [t.cpu().pin_memory() for t in (q, k, v)]
@@ -278,28 +497,47 @@ def main():
         for _ in range(args.e2e_steps):
             fa.attention_host(qh, kh, vh, main_causal, scale, bm, bn, device=local_rank, out=oh)
         barrier()
-        e2e_s = (time.perf_counter() - t0) / args.e2e_steps
-        if dist is not None:
-            t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_s = float(t.item())
+        e2e_s = reduce_max((time.perf_counter() - t0) / args.e2e_steps)
+        m = error_metrics(oh[:, :1], attention_fp32(qh[:, :1], kh[:, :1], vh[:, :1], main_causal, scale))
+        # what the copies alone cost on this box with all N ranks copying at once: the same bytes as plain
+        # pinned copies, both directions running together on two streams
+        s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        dst = [torch.empty_like(t) for t in (q, k, v)]
+        src_o = torch.empty_like(q)
+
+        def copies():
+            with torch.cuda.stream(s_in):
+                for d_, h_ in zip(dst, (qh, kh, vh)):
+                    d_.copy_(h_, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                oh.copy_(src_o, non_blocking=True)
+        copies()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            copies()
+        barrier()
+        floor_s = reduce_max((time.perf_counter() - t0) / args.e2e_steps)
         nbytes = q.numel() * 2
         e2e = {"value": flops / e2e_s / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_s * 1e3,
                "h2d_bytes_per_step": 3 * nbytes, "d2h_bytes_per_step": nbytes,
+               "copy_floor_ms": floor_s * 1e3,
+               "copy_floor_note": "the same bytes as plain pinned copies, H2D and D2H together on two streams, all "
+                                  "%d rank(s) at once; h2d %.1f GB/s per GPU" % (world, 3 * nbytes / floor_s / 1e9),
+               "parity_head0_ok": bool(m["finite"] and m["allclose"]),
                "api": "ascend_rsfa.flash_attention_forward.attention_host -> rsfa_fwd_host"}
-        del qh, kh, vh, oh
+        del qh, kh, vh, oh, dst, src_o
 
     if rank == 0:
-        peaks = load_peaks()
         per_gpu = value / world
+        record = config_record(args.config, cfg, main_causal)
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": "%s %s: B=%d H=%d S=%d D=%d sm_scale=%g, heads sharded over %d GPU(s)"
-                                   % (args.config, "causal" if main_causal else "non-causal", B, H, S, D, scale, world),
-                       "tile": [bm, bn], "l2": "inputs+outputs %.0f MiB per GPU, larger than the 126 MB L2"
-                                                % (4 * q.numel() * 2 / 2 ** 20)},
+            "config": record,
+            "sharding": "%d heads over %d GPU(s), %d on rank 0; no collective in the timed region" % (heads, world, n_local),
+            "tile": [bm, bn],
             "per_gpu_tflops": per_gpu,
             "pct_of_peak": {"measured_burst": per_gpu / peaks["burst"], "nominal_2250": per_gpu / 2250.0},
             "other_mask": {"causal": (not main_causal), "tflops": other_val, "ms_per_step": other_ms,
@@ -307,15 +545,24 @@ def main():
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["burst"], "unit": "TFLOP/s",
                          "frac": per_gpu / peaks["burst"],
                          "traffic": (NCU_DRAM_BYTES_PER_HEAD_S2048_D128 * n_local if (S, D) == (2048, 128) else None),
-                         "traffic_note": ("scaled from an ncu capture of 128 heads of this shape" if (S, D) == (2048, 128)
-                                          else "no ncu capture of this shape") + "; algorithmic bytes %.3e"
-                                         % (4.0 * n_local * S * D * 2),
-                         "peak_source": peaks["source"] + " cuBLAS bf16 burst; sustained %.1f" % peaks["sustained"],
-                         "frac_of_sustained": (per_gpu / peaks["sustained"]) if peaks["sustained"] else None},
+                         "traffic_source": (NCU_TRAFFIC_SOURCE + " (128 heads of this shape, scaled by the number of heads)"
+                                            if (S, D) == (2048, 128) else "no ncu capture of this shape"),
+                         "algorithmic_bytes": 4.0 * n_local * S * D * 2,
+                         "peak_source": peaks["source"] + " cuBLAS bf16 burst (the timed region is a burst at full "
+                                        "clock); sustained %.1f, see the `sustained` record" % peaks["sustained"]},
             "clocks": clocks.summary(),
             "gpu_launches": launches,
-            "parity": err,
+            "parity": par,
         }
+        if sustained is not None:
+            line["sustained"] = sustained
+        if launch_floor is not None:
+            line["launch_floor_us"] = launch_floor["us"]
+            line["launch_floor"] = launch_floor
+        if configs is not None:
+            line["configs"] = configs
+        if short_seq is not None:
+            line["short_seq"] = short_seq
         if e2e is not None:
             line["e2e"] = e2e
         if world == 1 and not args.no_cpu_baseline:

@@ -93,7 +93,10 @@ RSFA_API int rsfa_fwd_host(const void* q_host, const void* k_host, const void* v
  * of static device memory inside the library (held by every GPU that loads the library until the
  * process exits) and calls no cudaMalloc, cudaFree or other allocating routine.
  *
- * Arguments as rsfa_fwd, without block_m / block_n (the kernel has one tile).  Limits: only
+ * Arguments as rsfa_fwd, without block_m / block_n: the tile table decides, so either tcgen05
+ * kernel family may run (64-key tiles at D = 256 and for D = 128 causal around S = 1024, 128-key
+ * tiles otherwise; the D = 64 separate-P kernel, whose redo list is allocated scratch, is not used).
+ * Every in-kernel wait is bounded by the "wait_limit_ms" option, as in rsfa_fwd.  Limits: only
  * shapes the tcgen05 kernels are built for (sm_scale > 0; D = 16 and 32 run on the D = 64 kernel) -> otherwise
  * RSFA_ERR_UNSUPPORTED; at most 2^30 work items (B * H * ceil(S / 256), or ceil(S / 128) at D = 256), because the queue counter
  * is a single 32-bit word of the block -> otherwise RSFA_ERR_TOO_LARGE.
@@ -101,10 +104,11 @@ RSFA_API int rsfa_fwd_host(const void* q_host, const void* k_host, const void* v
  * The first call on a device looks up the device address of the static block (one
  * cudaGetSymbolAddress with that device current); make that first call outside any stream
  * capture.  All calls on a device share the one block, which keeps the previous call's contents:
- * each call clears the counter and the status word on `stream` before its kernel, so calls on one
- * stream are safe back to back, but two calls whose kernels can overlap on the GPU (different
- * streams, no dependency) race on the counter and must be ordered by the caller.  The status
- * word of this path is not exposed; a bounded wait that runs out leaves the output incomplete.
+ * each call clears the work queue and the status word on `stream` before its kernel, so calls on
+ * one stream are safe back to back, but two calls whose kernels can overlap on the GPU (different
+ * streams, no dependency) race on the queue and must be ordered by the caller.  A bounded wait
+ * that runs out leaves the output incomplete and a code in the block's status word, which
+ * rsfa_device_status reports together with rsfa_fwd's (the next rsfa_fwd_noalloc call clears it).
  */
 RSFA_API int rsfa_fwd_noalloc(const void* q, const void* k, const void* v, void* o, float* lse,
                               int B, int H, int S, int D, const int64_t* strides,
@@ -128,14 +132,29 @@ RSFA_API int rsfa_select_path(int S, int D, int causal, float sm_scale, int bloc
                      int* path, int* tile_m, int* tile_n);
 
 /*
+ * Number of work items rsfa_fwd splits this problem into: (batch, head, block of query rows) units
+ * that the persistent tcgen05 kernels hand out through their queue (256 rows each, 128 at D = 256),
+ * or the CTAs of the short-sequence kernel (64 rows each, all on grid.x, so the count may exceed
+ * 65535).  Counterpart of NUM_BLOCKS = cdiv(N_CTX, BLOCK_M) * Z * H (:289-294).  Needs no device.
+ */
+RSFA_API int rsfa_work_items(int B, int H, int S, int D, int causal, float sm_scale, long long* items);
+
+/*
  * Number of streaming multiprocessors of a device: the grid size of the persistent kernel.
  * Replaces get_num_compute_cores (:19-21).  Returns the count (> 0) or a negative error.
  */
 RSFA_API int rsfa_sm_count(int device);
 
 /*
- * Synchronise `device` and return the status word its kernels share: RSFA_OK, or
- * RSFA_ERR_DEVICE_STATUS with the raw word in *raw (if not NULL).  Reading clears the word.
+ * Synchronise `device` and return the status word its kernels share (this call allocates nothing
+ * and reads only the scratch that rsfa_fwd or rsfa_fwd_noalloc has already set up on the device): RSFA_OK, or
+ * RSFA_ERR_DEVICE_STATUS with the raw word in *raw (if not NULL): (1 << 16) | tag, where tag names
+ * the wait that ran out.  Reading clears the word.  rsfa_fwd itself returns RSFA_OK for a call
+ * whose kernel later gives up (the launch is asynchronous) and the output of that call is then
+ * incomplete: callers that care call this function at their synchronisation points, or set the
+ * "check_status" option, under which every rsfa_fwd copies the word to the host behind its kernels
+ * and the next rsfa_fwd on that device returns RSFA_ERR_DEVICE_STATUS without launching once a
+ * non-zero word has arrived (this function then reports and clears it).
  * The reference has no counterpart: its kernels cannot time out.
  */
 RSFA_API int rsfa_device_status(int device, int* raw);
@@ -150,7 +169,15 @@ RSFA_API long long rsfa_launch_count(void);
  * by a second launch over the work items it could not finish; 0 / 1 force the single-buffered 128-key /
  * double-buffered 64-key kernel for D <= 128; 2 forces 128-key tiles with the separate-P kernel where
  * it exists), "host_slab_heads"
- * (heads per staging slab of rsfa_fwd_host, 0 = automatic).
+ * (heads per staging slab of rsfa_fwd_host, 0 = automatic), "pdl" (1, the default: the tcgen05 kernels
+ * are launched with programmatic stream serialisation, so the set-up of a launch overlaps the tail of
+ * the kernel in front of it on the stream; they wait for that kernel before touching global memory),
+ * "check_status" (0 / 1, see rsfa_device_status), "test_drop_load" (-1 = off; n >= 0: every CTA of the
+ * 128-key tcgen05 kernel leaves out its n-th K/V tile load and the barrier arrival that announces it,
+ * so that a bounded wait runs out - for tests of the wait-expired path; the output of such a call
+ * is incomplete).
+ * rsfa_get_option also answers "workspace_devices": the number of devices on which rsfa_fwd has
+ * created its workspace (0 in a process that has only used rsfa_fwd_noalloc).
  * Unknown names -> RSFA_ERR_INVALID_ARGUMENT.
  */
 RSFA_API int rsfa_set_option(const char* name, long long value);

@@ -255,6 +255,169 @@ def test_head_dim_256_shapes(fa, cuda_device, causal):
     check(fa, q, k, v, causal, 0.5, 64, 256, cuda_device)
 
 
+# ---- the benchmark configurations' own per-head shapes (cfg4: S=4096, D=128, sm_scale=1/sqrt(128);
+# cfg5: S=8192, D=64, inputs x 2.0, sm_scale=1/8), a few heads each, both masks.  The reference runs
+# S=8192, D=64 among its paper shapes (flash_attention_forward.py:743-756,
+# benchmarks/run_correctness_test.py:142-148).
+_ORACLE_CACHE = {}
+
+
+def _oracle(name, B, H, causal):
+    key = (name, B, H, causal)
+    if key not in _ORACLE_CACHE:
+        _, _, S, D, scale, mult = CONFIGS[name]
+        q, k, v = make_inputs(B, H, S, D, seed=42, std=mult)
+        _ORACLE_CACHE[key] = (q, k, v) + attention_fp32(q, k, v, causal, scale, return_lse=True)
+    return _ORACLE_CACHE[key]
+
+
+def _check_config_shape(fa, dev, name, B, H, causal, bm, bn):
+    _, _, S, D, scale, _ = CONFIGS[name]
+    q, k, v, ref, lse_ref = _oracle(name, B, H, causal)
+    o, M = fa.attention_with_lse(q.to(dev), k.to(dev), v.to(dev), causal, scale, bm, bn)
+    torch.cuda.synchronize()
+    fa.device_status()
+    m = error_metrics(o, ref, ATOL, RTOL)
+    # error relative to the magnitude of the output: with inputs x 2 (cfg5) rows are close to one-hot
+    # and |O| reaches 8 and more, where one fp16 step of the OUTPUT is 2^-7 = 7.8e-3; the absolute
+    # error then is a few 1e-3 although every element is within about one fp16 step of the oracle.
+    scaled = float(((o.float().cpu() - ref).abs() / ref.abs().clamp_min(1.0)).max())
+    print("%s S=%d D=%d causal=%s tile=(%d,%d): max_abs %.3e, max |err|/max(1,|ref|) %.3e, max |ref| %.2f"
+          % (name, S, D, causal, bm, bn, m["max_abs"], scaled, float(ref.abs().max())))
+    assert m["finite"] and m["allclose"], m
+    assert scaled < 2e-3, (m, scaled)
+    assert torch.allclose(M.cpu(), lse_ref, atol=2e-3, rtol=2e-3)
+    return m
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_cfg4_shape_long_sequence_d128(fa, cuda_device, causal):
+    bm, bn = fa.get_tiling(16, 16, 4096, 128, causal)
+    m = _check_config_shape(fa, cuda_device, "cfg4", 2, 4, causal, bm, bn)
+    assert m["max_abs"] < 4e-3, m          # N(0,1) inputs: outputs of order 1
+    _check_config_shape(fa, cuda_device, "cfg4", 2, 4, causal, 128, 64)   # the 64-key kernel at 64 key tiles per row
+
+
+@pytest.mark.parametrize("variant", [-1, 0, 1, 2])
+@pytest.mark.parametrize("causal", [False, True])
+def test_cfg5_shape_very_long_small_head_wide_logits(fa, cuda_device, causal, variant):
+    # 64 key tiles of 128 per row; variant -1 / 2 = separate-P kernel + redo pass, 0 = 128-key kernel
+    # alone, 1 = 64-key kernel.  Inputs x 2.0 widen the logits (std 5.8 log2 units).
+    fa.set_option("tcgen05_variant", variant)
+    try:
+        n0 = fa.launch_count()
+        _check_config_shape(fa, cuda_device, "cfg5", 1, 4, causal, 128, 128)
+        assert fa.launch_count() - n0 == (2 if variant in (-1, 2) else 1)
+    finally:
+        fa.set_option("tcgen05_variant", -1)
+
+
+def test_more_heads_than_a_grid_dimension_on_the_short_sequence_kernel(fa, cuda_device):
+    # 8192 x 16 = 131072 heads of S=64, D=64: the short-sequence kernel keeps its heads on grid.x
+    # (gridDim.y would stop at 65535).  q = k = 0 gives uniform weights, v = 1 gives O = 1 everywhere.
+    from ascend_rsfa import _capi
+
+    B, H, S, D = 8192, 16, 64, 64
+    assert fa.select_path(S, D, False, 0.5)[0] == _capi.RSFA_PATH_GENERIC
+    items = ctypes.c_longlong(0)
+    assert _capi.load().rsfa_work_items(B, H, S, D, 0, 0.5, ctypes.byref(items)) == 0 and items.value == B * H
+    z = torch.zeros(B, H, S, D, dtype=torch.float16, device=cuda_device)
+    v = torch.ones_like(z)
+    v[-1, -1] = 3.0                      # the very last head is told apart
+    for causal in (False, True):
+        o = fa.attention(z, z, v, causal, 0.5, 64, 64)
+        torch.cuda.synchronize()
+        assert bool((o[:-1] == 1).all()) and bool((o[-1, :-1] == 1).all()) and bool((o[-1, -1] == 3).all())
+    del z, v, o
+    torch.cuda.empty_cache()
+
+
+def test_bounded_wait_runs_out_and_is_reported(fa, cuda_device):
+    """The wait-expired path on a healthy GPU: the producer leaves out one K/V tile load together
+    with the barrier arrival that would announce it (the "test_drop_load" option), so nothing is in
+    flight and no address is touched; the MMA warp's wait for that tile runs out after
+    `wait_limit_ms`, every role of the CTA leaves, tensor memory is freed and the kernel returns by
+    itself with (1 << 16) | tag in the status word."""
+    from ascend_rsfa import _capi
+
+    lib = _capi.load()
+    q, k, v = [t.to(cuda_device) for t in make_inputs(1, 1, 256, 128, seed=3)]
+    ref = attention_fp32(q.cpu(), k.cpu(), v.cpu(), False, 0.5)
+    fa.device_status()                                   # clean before the experiment
+    fa.set_option("wait_limit_ms", 1)
+    fa.set_option("test_drop_load", 1)                   # load 0 = K_0, load 1 = V_0
+    try:
+        fa.attention(q, k, v, False, 0.5, 128, 128)      # returns normally: the launch is asynchronous
+        torch.cuda.synchronize()
+    finally:
+        fa.set_option("test_drop_load", -1)
+        fa.set_option("wait_limit_ms", 2000)
+    raw = ctypes.c_int(0)
+    rc = lib.rsfa_device_status(0, ctypes.byref(raw))
+    assert rc == _capi.RSFA_ERR_DEVICE_STATUS
+    assert (raw.value >> 16) == 1 and 1 <= (raw.value & 0xffff) <= 10, hex(raw.value)
+    assert lib.rsfa_device_status(0, ctypes.byref(raw)) == _capi.RSFA_OK and raw.value == 0   # reading cleared it
+    # the context is intact and the next ordinary calls are correct (the work queue was left clean)
+    for _ in range(2):
+        o = fa.attention(q, k, v, False, 0.5, 128, 128)
+        torch.cuda.synchronize()
+        m = error_metrics(o, ref)
+        assert m["finite"] and m["allclose"], m
+    fa.device_status()
+
+
+def test_check_status_option_makes_the_next_call_fail(fa, cuda_device):
+    """With "check_status" on, the status word travels to the host behind every call and the next
+    call on the device refuses to launch once a non-zero word has arrived; device_status() raises
+    with the word and clears it, after which calls work again."""
+    q, k, v = [t.to(cuda_device) for t in make_inputs(1, 1, 256, 128, seed=4)]
+    ref = attention_fp32(q.cpu(), k.cpu(), v.cpu(), True, 0.5)
+    fa.device_status()
+    fa.set_option("check_status", 1)
+    fa.set_option("wait_limit_ms", 1)
+    fa.set_option("test_drop_load", 1)
+    try:
+        fa.attention(q, k, v, True, 0.5, 128, 128)
+        torch.cuda.synchronize()
+        fa.set_option("test_drop_load", -1)
+        fa.set_option("wait_limit_ms", 2000)
+        with pytest.raises(RuntimeError, match="device status"):
+            fa.attention(q, k, v, True, 0.5, 128, 128)
+        with pytest.raises(RuntimeError, match="device status 0x1000"):
+            fa.device_status()
+        o = fa.attention(q, k, v, True, 0.5, 128, 128)
+        torch.cuda.synchronize()
+        m = error_metrics(o, ref)
+        assert m["finite"] and m["allclose"], m
+    finally:
+        fa.set_option("test_drop_load", -1)
+        fa.set_option("wait_limit_ms", 2000)
+        fa.set_option("check_status", 0)
+    fa.device_status()
+
+
+def test_d64_calls_on_several_streams_do_not_share_redo_scratch(fa, cuda_device):
+    # At D = 64 a call is two launches that share a scratch block (marks of the work items to run
+    # again).  Calls that are in flight at the same time on different streams must each get a block
+    # of their own, or run the kernel that needs none: near one-hot rows (sm_scale 3) mark many items,
+    # so a block shared by two calls would lose marks and leave wrong output.
+    q, k, v = make_inputs(2, 3, 1024, 64, seed=31)
+    ref = {c: attention_fp32(q, k, v, c, 3.0) for c in (False, True)}
+    qd, kd, vd = [t.to(cuda_device) for t in (q, k, v)]
+    streams = [torch.cuda.Stream(device=cuda_device) for _ in range(3)]
+    torch.cuda.synchronize()
+    outs = []
+    for i in range(24):
+        causal = bool(i & 1)
+        with torch.cuda.stream(streams[i % 3]):
+            outs.append((causal, fa.attention(qd, kd, vd, causal, 3.0, 128, 128)))
+    torch.cuda.synchronize()
+    fa.device_status()
+    for causal, o in outs:
+        m = error_metrics(o, ref[causal])
+        assert m["finite"] and m["allclose"], m
+
+
 def test_strided_inputs_and_views(fa, cuda_device):
     B, H, S, D = 2, 3, 256, 64
     big = torch.randn(B, S, 3, H, D, generator=torch.Generator().manual_seed(1)).half()
@@ -268,6 +431,17 @@ def test_strided_inputs_and_views(fa, cuda_device):
     m = error_metrics(o, ref)
     assert m["finite"] and m["allclose"], m
     assert o.shape == (B, H, S, D)
+    # a batch of one whose (meaningless) batch stride is odd: PyTorch calls such a view contiguous and
+    # passes it on unchanged; the tensor maps must not take that stride at face value
+    base = torch.randn(1 * 2 * 300 * 128 + 3, generator=torch.Generator().manual_seed(2)).half().to(dev)
+    for off in (0,):
+        t = torch.as_strided(base, (1, 2, 300, 128), (2 * 300 * 128 + 3, 300 * 128, 128, 1), off)
+        assert t.is_contiguous()
+        o = fa.attention(t, t, t, False, 0.1, 128, 128)
+        torch.cuda.synchronize()
+        tc = t.cpu().contiguous()
+        m = error_metrics(o, attention_fp32(tc, tc, tc, False, 0.1))
+        assert m["finite"] and m["allclose"], m
 
 
 def test_requires_grad_inputs_and_no_backward(fa, cuda_device):

@@ -136,3 +136,51 @@ def test_tile_table_is_total_and_consistent():
         assert fa.get_tiling(1, 1, 100, D, True) == (64, 64)                              # short-sequence path
     for S in (1, 64, 128):
         assert fa.get_tiling(1, 1, S, 128, False) == (64, 64)      # short-sequence path
+
+
+def test_work_items_need_no_device_and_count_every_head():
+    items = ctypes.c_longlong(0)
+    f = lib.rsfa_work_items
+    # tcgen05 kernels: blocks of 256 query rows (128 at D = 256) per (batch, head)
+    assert f(128, 8, 2048, 128, 0, 0.5, ctypes.byref(items)) == 0 and items.value == 1024 * 8
+    assert f(64, 8, 1024, 256, 1, 0.0625, ctypes.byref(items)) == 0 and items.value == 512 * 8
+    assert f(4, 32, 8192, 64, 0, 0.125, ctypes.byref(items)) == 0 and items.value == 128 * 32
+    # short-sequence kernel: one CTA per 64 rows, all on grid.x - more heads than gridDim.y could hold
+    assert f(8192, 16, 64, 64, 0, 0.5, ctypes.byref(items)) == 0 and items.value == 131072
+    assert f(70000, 1, 100, 16, 1, 0.5, ctypes.byref(items)) == 0 and items.value == 140000
+    assert f(1, 2, 128, 64, 0, 0.5, ctypes.byref(items)) == 0 and items.value == 4
+    assert f(1, 1, 0, 64, 0, 0.5, ctypes.byref(items)) == _capi.RSFA_ERR_INVALID_ARGUMENT
+    assert f(1, 1, 64, 64, 0, 0.5, None) == _capi.RSFA_ERR_INVALID_ARGUMENT
+
+
+def test_new_options_round_trip():
+    for name, good, bad in (("pdl", (0, 1), 2), ("check_status", (1, 0), -1), ("test_drop_load", (5, -1), -2)):
+        for v in good:
+            fa.set_option(name, v)
+            assert lib.rsfa_get_option(name.encode()) == v
+        with pytest.raises(ValueError):
+            fa.set_option(name, bad)
+    assert lib.rsfa_get_option(b"workspace_devices") == 0      # no device call has been made here
+    with pytest.raises(ValueError):
+        fa.set_option("workspace_devices", 1)                   # read-only
+
+
+def test_build_staleness_is_decided_by_content_not_by_file_times(tmp_path):
+    import importlib.util
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("rsfa_build", os.path.join(root, "ascend-rsfa_b200", "build.py"))
+    b = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(b)
+    h = b.source_hash(b.FLAGS)
+    assert h == b.source_hash(list(b.FLAGS)) and h != b.source_hash(b.FLAGS + ["-DRSFA_TRACE"])
+    out = tmp_path / "lib.so"
+    assert b.stale(str(out), b.FLAGS)                            # nothing built yet
+    out.write_bytes(b"x")
+    assert b.stale(str(out), b.FLAGS)                            # a library without a stamp
+    (tmp_path / "lib.so.stamp").write_text(h + "\n")
+    os.utime(out, (1, 1))                                        # an ancient file time changes nothing
+    assert not b.stale(str(out), b.FLAGS)
+    (tmp_path / "lib.so.stamp").write_text("0" * 64 + "\n")
+    assert b.stale(str(out), b.FLAGS)                            # built from other sources

@@ -12,6 +12,9 @@ The file name sorts last on purpose: a run that stops at the first failure has t
 executed every other test.
 """
 import ctypes
+import os
+import subprocess
+import sys
 
 import pytest
 import torch
@@ -95,3 +98,64 @@ def test_noalloc_rejects_what_it_cannot_serve(cuda_device):
     rc = lib.rsfa_fwd_noalloc(None, q.data_ptr(), q.data_ptr(), o.data_ptr(), None, 1, 1, 256, 64, st, 0, 0.5,
                               _capi.RSFA_DTYPE_F16, None)
     assert rc == _capi.RSFA_ERR_INVALID_ARGUMENT
+
+
+_FRESH_PROCESS = r"""
+import ctypes, sys
+sys.path.insert(0, sys.argv[1])
+import torch
+from ascend_rsfa import _capi
+lib = _capi.load()
+dev = torch.device("cuda:0")
+torch.cuda.init()
+g = torch.Generator(device=dev).manual_seed(7)
+B, H, S, D = 2, 2, 512, 128
+q, k, v = [torch.randn(B, H, S, D, generator=g, device=dev).half() for _ in range(3)]
+o = torch.empty_like(q)
+st = (ctypes.c_int64 * 16)(*(list(q.stride()) * 4))
+stream = torch.cuda.current_stream().cuda_stream
+def call():
+    rc = lib.rsfa_fwd_noalloc(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), None, B, H, S, D, st, 1, 0.25,
+                              _capi.RSFA_DTYPE_F16, stream)
+    assert rc == 0, _capi.strerror(rc)
+    torch.cuda.synchronize()
+call()                                   # first library call of the process: symbol look-up, module load
+free0, _ = torch.cuda.mem_get_info(dev)
+call()
+call()
+free1, _ = torch.cuda.mem_get_info(dev)
+assert free0 == free1, (free0, free1)    # the driver handed out nothing in between
+assert lib.rsfa_get_option(b"workspace_devices") == 0      # rsfa_fwd's lazily allocated workspace was never made
+raw = ctypes.c_int(-1)
+assert lib.rsfa_device_status(0, ctypes.byref(raw)) == 0 and raw.value == 0
+assert lib.rsfa_get_option(b"workspace_devices") == 0      # asking for the status allocates nothing either
+free2, _ = torch.cuda.mem_get_info(dev)
+assert free2 == free0, (free0, free2)
+# an expired wait on this path is visible: the status word of the static block is reported too
+lib.rsfa_set_option(b"wait_limit_ms", 1)
+lib.rsfa_set_option(b"test_drop_load", 1)
+call()
+lib.rsfa_set_option(b"test_drop_load", -1)
+lib.rsfa_set_option(b"wait_limit_ms", 2000)
+rc = lib.rsfa_device_status(0, ctypes.byref(raw))
+assert rc == _capi.RSFA_ERR_DEVICE_STATUS and (raw.value >> 16) == 1, (rc, hex(raw.value))
+ref = torch.empty_like(q)
+call()                                   # and the next call is whole again
+o_after = o.clone()
+rc = lib.rsfa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), ref.data_ptr(), None, B, H, S, D, st, 1, 0.25, 128, 128,
+                  _capi.RSFA_DTYPE_F16, stream)
+torch.cuda.synchronize()
+assert rc == 0 and torch.equal(o_after, ref)
+assert lib.rsfa_get_option(b"workspace_devices") == 1      # that was rsfa_fwd: now the workspace exists
+print("noalloc-fresh-process-ok")
+"""
+
+
+def test_noalloc_allocates_nothing_in_a_fresh_process(cuda_device):
+    """The property the entry point exists for, checked where nothing else has warmed anything up:
+    in a new process rsfa_fwd_noalloc is the first call into the library; after that first call
+    (symbol look-up, lazy loading of the kernel image) the free device memory reported by the driver
+    is the same before and after further calls, and rsfa_fwd's own workspace was never created."""
+    pkg = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "ascend-rsfa_b200")
+    r = subprocess.run([sys.executable, "-c", _FRESH_PROCESS, pkg], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "noalloc-fresh-process-ok" in r.stdout, r.stdout + r.stderr
