@@ -287,8 +287,9 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         // of 16 along D moves the start address by 32 B inside the 128-byte swizzle row.
         // The MMAs of one operand pair and the commits that follow them are issued from ONE elected
         // region: an elect.sync and a branch per instruction cost the issuing warp more than the
-        // instruction (batched: +3 % at D = 128, +4 % at D = 64).  commit_a / commit_b = 0: none.
-        auto issue_qk = [&](int t, uint32_t kslot, uint32_t commit_a, uint32_t commit_b) {
+        // instruction (batched: +3 % at D = 128, +4 % at D = 64).  A commit of 0 means none.
+        auto issue_qk = [&](int t, uint32_t kslot, uint32_t commit_a, uint32_t commit_b, uint32_t commit_c = 0u,
+                            uint32_t commit_d = 0u) {
           const uint64_t qd = desc_q0 + static_cast<uint64_t>((t * C::kQTileBytes) >> 4);
           const uint64_t kd = desc_k0 + static_cast<uint64_t>((kslot * C::kKvTileBytes) >> 4);
           if (elect_one()) {
@@ -300,6 +301,8 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
             }
             if (commit_a != 0) umma_commit(commit_a);
             if (commit_b != 0) umma_commit(commit_b);
+            if (commit_c != 0) umma_commit(commit_c);
+            if (commit_d != 0) umma_commit(commit_d);
           }
           __syncwarp();
         };
@@ -340,13 +343,56 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
           }
           umma_commit_elect(bar_kv_empty(base % C::kStages));
         }
-        for (int j = 0; ok && j < nmax; ++j) {
+        // Steady state, kept free of everything the end of an item needs: while both tiles have key tiles
+        // left after step j, every step is V_j, then per tile PV(j) in two halves and QK^T(j+1).  The MMA
+        // warp is the pacemaker of the CTA: an extra test or call in this loop shows up in every step.
+        const int n_lean = min(n[0], n[1]) - 1;
+        int j0 = 0;
+        for (; ok && j0 < n_lean; ++j0) {
+          const uint32_t vidx = base + 2 * j0 + 1;
+          const uint32_t kidx = base + 2 * j0 + 2;
+          const uint32_t vslot = vidx % C::kStages, kslot = kidx % C::kStages;
+          ok = wait_kv(vidx);
+          if (!ok) break;
+          RSFA_TRACE_EV(0x6000 + j0);                  // V_j present
+#pragma unroll
+          for (int t = 0; t < kNT; ++t) {
+            ok = wait_all(bar_p_full(t, 0), p_count[t] & 1, kTagPFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            RSFA_TRACE_EV(0x1000 + (t << 8) + j0);   // P half 0 seen
+            issue_pv(t, vslot, j0 > 0, 0, kTileN / 32, bar_pv0_done(t));
+            RSFA_TRACE_EV(0x2000 + (t << 8) + j0);   // PV half 0 issued
+            ok = wait_all(bar_p_full(t, 1), p_count[t] & 1, kTagPFull);
+            if (!ok) break;
+            ++p_count[t];
+            tc_fence_after_sync();
+            RSFA_TRACE_EV(0x3000 + (t << 8) + j0);   // P half 1 seen
+            issue_pv(t, vslot, true, kTileN / 32, kTileN / 16, 0u);
+            RSFA_TRACE_EV(0x4000 + (t << 8) + j0);   // PV half 1 issued
+            if (t == 0) {
+              ok = wait_kv(kidx);
+              if (!ok) break;
+              tc_fence_after_sync();
+            }
+            RSFA_TRACE_EV(0x9000 + (t << 8) + j0);   // K ready
+            // behind the last MMAs of the step that read V_j and K_{j+1} the release of both slots rides along
+            issue_qk(t, kslot, bar_s_full(t), j0 + 2 == n[t] ? bar_q_empty(t) : 0u,
+                     t == kNT - 1 ? bar_kv_empty(vslot) : 0u, t == kNT - 1 ? bar_kv_empty(kslot) : 0u);
+            RSFA_TRACE_EV(0x5000 + (t << 8) + j0);   // QK(j+1) and its commits issued
+          }
+          RSFA_TRACE_EV(0x7000 + j0);   // iteration end
+        }
+        if (!ok) break;
+        // The last steps of the item, in which a tile may run out of key tiles (both at once without the
+        // causal mask, one a step before the other with it).
+        for (int j = j0; ok && j < nmax; ++j) {
           const uint32_t vidx = base + 2 * j + 1;
           const uint32_t kidx = base + 2 * j + 2;
           ok = wait_kv(vidx);
           if (!ok) break;
           RSFA_TRACE_EV(0x6000 + j);                  // V_j present
-          bool k_ready = false;
+          bool k_ready = false, folded = false;
           for (int t = 0; ok && t < kNT; ++t) {
             if (j < n[t]) {
               ok = wait_all(bar_p_full(t, 0), p_count[t] & 1, kTagPFull);
@@ -371,7 +417,9 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
                 k_ready = true;
               }
               RSFA_TRACE_EV(0x9000 + (t << 8) + j);   // K ready
-              issue_qk(t, kidx % C::kStages, bar_s_full(t), j + 2 == n[t] ? bar_q_empty(t) : 0u);
+              folded = (t == kNT - 1);   // the last MMAs of the step: the release of both slots rides along
+              issue_qk(t, kidx % C::kStages, bar_s_full(t), j + 2 == n[t] ? bar_q_empty(t) : 0u,
+                       folded ? bar_kv_empty(vidx % C::kStages) : 0u, folded ? bar_kv_empty(kidx % C::kStages) : 0u);
               RSFA_TRACE_EV(0x5000 + (t << 8) + j);   // QK(j+1) and its commits issued
             }
           }
@@ -380,7 +428,8 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
             ok = wait_kv(kidx);
             if (!ok) break;
           }
-          umma_commit2_elect(bar_kv_empty(vidx % C::kStages), j + 1 < nmax ? bar_kv_empty(kidx % C::kStages) : 0u);
+          if (!folded)
+            umma_commit2_elect(bar_kv_empty(vidx % C::kStages), j + 1 < nmax ? bar_kv_empty(kidx % C::kStages) : 0u);
           RSFA_TRACE_EV(0x7000 + j);   // iteration end
         }
         if (!ok) break;

@@ -238,8 +238,8 @@ __device__ __forceinline__ void store_o_rows(uint32_t t_o, float inv_l, uint32_t
 // allocates 168 per thread): two softmax warpgroups and the warpgroup of the TMA / MMA warps.
 // setmaxnreg.inc can only take registers that another warpgroup of the same CTA has released with
 // setmaxnreg.dec: an increase that asks for more than was released waits for ever (it did, with
-// 208 / 96).  D = 128: 200 / 104 (the MMA warp no longer spills; +1 % over 208 / 80); D = 64:
-// 208 / 80 (200 / 104 is 6 % slower there).
+// 208 / 96).  D = 128: 200 / 104 (184 / 136 and 168 / 168 measure the same: the softmax does not need
+// more than 168); D = 64: 208 / 80 (200 / 104 is 6 % slower there).
 template <int D>
 struct RegBudget {
   static constexpr int kLaunch = 168;
