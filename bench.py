@@ -23,7 +23,7 @@ Prints ONE JSON line on rank 0.  Keys beyond the basic contract:
                      checksums must equal the ones each rank computed locally
   configs            the other benchmark configurations (cfg3, cfg4, cfg5), both masks, 20 steps each
   short_seq          (N = 1) the HBM-bound short-sequence shapes as bytes / time against the measured copy rate
-  launch_floor_us    (N = 1) what one launch costs beyond its work items: t(1 wave) - (t(2 waves) - t(1 wave))
+  launch_floor_us    (N = 1) what one launch costs beyond its work items, from CUDA-graph replays of a small problem
   e2e                the same metric through `attention_host()` with pinned host tensors (host->device and
                      device->host copies inside the timed region), with the plain-copy floor of the box beside it
   cpu_baseline       (N = 1) the fp32 reference math on the host cores for a bounded sample
@@ -54,6 +54,7 @@ NCU_DRAM_BYTES_PER_HEAD_S2048_D128 = 249.4e6 / 128
 NCU_TRAFFIC_SOURCE = "profiles/fwd_tcgen05_d128_s2048_ncu_full.md"
 # Peaks used only when MEASURED_PEAKS.json is absent: cuBLAS bf16 burst / sustained TFLOP/s and copy GB/s.
 FALLBACK_PEAKS = {"burst": 1590.0, "sustained": 1400.0, "hbm_gbs": 6650.0}
+IDLE_BEFORE_TIMING_S = 1.0
 
 
 def parse_args():
@@ -162,6 +163,7 @@ def config_record(name, cfg, causal):
     B, H, S, D, _, _ = cfg
     mib = 4.0 * B * H * S * D * 2 / 2 ** 20
     return {"workload": workload_name(name, cfg, causal), "inputs": "fp16 i.i.d. N(0,1) from a seed, [B,H,S,D] contiguous",
+            "timing": "CUDA events around the timed steps, after %g s of idle and the warm-up steps" % IDLE_BEFORE_TIMING_S,
             "l2": "inputs+outputs %.0f MiB per step, %s the 126 MB L2" % (mib, "larger than" if mib > 126 else "NOT larger than")}
 
 
@@ -299,6 +301,9 @@ def main():
         B, H, S, D, scale, _ = c
         q, k, v = tensors
         bm, bn = fa.get_tiling(B, H, S, D, causal)   # the table's tile for this mask
+        # every timed region starts from the same state: a second of idle lets the power cap's average
+        # settle, so a region that follows another one is not measured at the clocks the first left behind
+        time.sleep(IDLE_BEFORE_TIMING_S)
         for _ in range(warmup):
             fa.attention(q, k, v, causal, scale, bm, bn)
         barrier()
@@ -379,18 +384,45 @@ def main():
     extras = not args.no_extras
     sustained = None
     # ------------------------------------------------------------------ launch floor (N = 1)
+    # What one launch costs beyond its work items, on the GPU alone: 100 launches of a small problem are
+    # captured in a CUDA graph (the host cannot issue 10 us kernels fast enough through Python) and
+    # replayed; with one work item per SM and with two, floor = 2 t(1) - t(2).  The replays last a
+    # millisecond, so both run at the same full clock.
     launch_floor = None
     if extras and world == 1:
-        sms = fa.get_num_compute_cores()
-        lf_cfg = lambda nh: (1, nh, 1024, 128, 0.5, 1.0)     # 4 work items of 256 rows per head
-        h1 = max(1, sms // 4)
-        t = {}
-        for waves in (1, 2):
-            c = lf_cfg(h1 * waves)
-            t[waves], _, _ = timed(c, make_slab(c, 7), False, 200, 20)
-        launch_floor = {"us": (2 * t[1] - t[2]) * 1e3, "t_one_wave_us": t[1] * 1e3, "t_two_waves_us": t[2] * 1e3,
-                        "shape": "S=1024 D=128 non-causal, %d and %d heads = 1 and 2 work items per SM, 200 "
-                                 "back-to-back launches each" % (h1, 2 * h1)}
+        try:
+            sms = fa.get_num_compute_cores()
+            per_graph = 100
+            t = {}
+            for mult in (1, 2):
+                c = (1, (sms // 2) * mult, 512, 128, 0.5, 1.0)      # 2 work items of 256 rows per head
+                lq, lk, lv = make_slab(c, 7)
+                lbm, lbn = fa.get_tiling(c[0], c[1], c[2], c[3], False)
+                for _ in range(3):
+                    fa.attention(lq, lk, lv, False, c[4], lbm, lbn)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    for _ in range(per_graph):
+                        fa.attention(lq, lk, lv, False, c[4], lbm, lbn)
+                graph.replay()
+                torch.cuda.synchronize()
+                time.sleep(0.5)
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
+                for _ in range(3):
+                    graph.replay()
+                ev1.record()
+                torch.cuda.synchronize()
+                t[mult] = ev0.elapsed_time(ev1) / (3 * per_graph)
+                del graph
+            launch_floor = {"us": (2 * t[1] - t[2]) * 1e3, "t_1_item_per_sm_us": t[1] * 1e3,
+                            "t_2_items_per_sm_us": t[2] * 1e3,
+                            "shape": "S=512 D=128 non-causal, %d and %d heads = 1 and 2 work items per SM; %d launches "
+                                     "per CUDA graph, 3 replays; floor = 2 t(1) - t(2)" % (sms // 2, sms, per_graph)}
+            fa.device_status()
+        except Exception as e:   # a capture problem must not cost the whole benchmark line
+            launch_floor = {"us": None, "error": repr(e)[:200]}
 
     # ------------------------------------------------------------------ the other benchmark configurations
     configs = None
@@ -420,43 +452,8 @@ def main():
     # ------------------------------------------------------------------ short sequences: HBM-bound (N = 1)
     short_seq = None
     if extras and world == 1 and args.batch == 0:
-        short_seq = []
-        for (sB, sH, sS, sD, sscale, bmn) in ((1, 2, 128, 64, 0.5, (64, 64)), (4, 32, 64, 64, 0.5, (64, 64)),
-                                               (4, 32, 128, 128, 0.5, (64, 64)), (512, 8, 128, 128, 0.5, (128, 128))):
-            nbytes = 4 * sB * sH * sS * sD * 2
-            # input sets rotated through a pool of at least 300 MB (the L2 holds 126 MB)
-            sets = int(max(2, min(8192, (300 << 20) // (3 * nbytes // 4) + 1)))
-            g = torch.Generator(device=dev).manual_seed(5)
-            pool = torch.randn((sets, 3, sB, sH, sS, sD), generator=g, device=dev, dtype=torch.float16)
-            views = [(pool[i, 0], pool[i, 1], pool[i, 2]) for i in range(sets)]
-            n_it = 400
-            for causal in (False,):
-                for i in range(10):
-                    fa.attention(*views[i % sets], causal, sscale, *bmn)
-                torch.cuda.synchronize()
-                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                ev0.record()
-                for i in range(n_it):
-                    fa.attention(*views[i % sets], causal, sscale, *bmn)
-                ev1.record()
-                torch.cuda.synchronize()
-                us = ev0.elapsed_time(ev1) / n_it * 1e3
-                # the tcgen05 kernels take 256 query rows per work item, the short-sequence kernel 64
-                path = 1 if (sS > 64 and fa.work_items(sB, sH, sS, sD, causal, sscale) == sB * sH) else 0
-                o = fa.attention(pool[0, 0], pool[0, 1], pool[0, 2], causal, sscale, *bmn)
-                torch.cuda.synchronize()
-                sel = spread(sB * sH, 8)
-                flat = lambda x: x.reshape(1, sB * sH, sS, sD)[:, sel]
-                m = error_metrics(flat(o), attention_fp32(flat(pool[0, 0]).cpu(), flat(pool[0, 1]).cpu(),
-                                                          flat(pool[0, 2]).cpu(), causal, sscale))
-                short_seq.append({"shape": [sB, sH, sS, sD], "causal": causal, "us_per_call": us,
-                                  "bytes_per_call": nbytes, "gb_per_s": nbytes / (us * 1e-6) / 1e9,
-                                  "frac_of_measured_hbm": nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
-                                  "kernel": "tcgen05 (one key tile per work item)" if path == 1 else "short-sequence (mma.sync)",
-                                  "input_sets_rotated": sets,
-                                  "parity": {"ok": bool(m["finite"] and m["allclose"]), "heads": len(sel),
-                                             "max_abs": m["max_abs"]}})
-            del pool, views
+        from benchmarks import short_seq as ss
+        short_seq = [ss.measure(fa, dev, peaks["hbm_gbs"], shape) for shape in ss.SHAPES]
         fa.device_status()
 
     # ------------------------------------------------------------------ sustained clock regime (N = 1)
