@@ -267,6 +267,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))   # the oracle checks run on the host cores
     peaks = load_peaks()
 
     def barrier():
