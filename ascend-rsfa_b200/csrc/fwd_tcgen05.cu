@@ -192,9 +192,17 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         ok = mbar_wait(bar_sched_empty0 + 8u * slot, ((item_count >> 1) & 1) ^ 1, abort_flag, wait_ns,
                        kTagSched);
         if (!ok) break;
-        int item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
-        if (sched.redo_count != nullptr)
+        // The first item of a CTA is its own index (the grid is never larger than the number of items): no
+        // round trip to the queue stands before the first loads.  The queue hands out the items behind those.
+        int item;
+        if (sched.redo_count != nullptr) {
+          item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
           item = (item < *sched.redo_count) ? sched.redo_list[item] : sched.total_items;
+        } else if (item_count == 0) {
+          item = static_cast<int>(blockIdx.x);
+        } else {
+          item = static_cast<int>(atomicAdd(p.tile_counter, 1u) + gridDim.x);
+        }
         sched_ring[slot] = item;
         __threadfence_block();
         mbar_arrive(bar_sched_full0 + 8u * slot);

@@ -191,7 +191,9 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         int item = claimed;
         claimed = -1;
         if (item < 0) {
-          item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
+          // the first item of a CTA is its own index (grid <= number of items), the queue hands out the rest
+          item = (item_count == 0) ? static_cast<int>(blockIdx.x)
+                                   : static_cast<int>(atomicAdd(p.tile_counter, 1u) + gridDim.x);
           if (C::kQTmem) prefetch_q(item);
         }
         sched_ring[slot] = item;
@@ -225,7 +227,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         };
         if constexpr (C::kQTmem) {
           if (!p.causal) {
-            claimed = static_cast<int>(atomicAdd(p.tile_counter, 1u));
+            claimed = static_cast<int>(atomicAdd(p.tile_counter, 1u) + gridDim.x);
             prefetch_q(claimed);
           }
           // Q is the first ring entry of the item

@@ -163,7 +163,9 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           // more than the 128-key kernel alone would have.  The first kBailRounds items of every CTA always run.
           int item;
           for (;;) {
-            item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
+            // the first item of a CTA is its own index (grid <= number of items), the queue hands out the rest
+            item = (item_count == 0) ? static_cast<int>(blockIdx.x)
+                                     : static_cast<int>(atomicAdd(p.tile_counter, 1u) + gridDim.x);
             if (item >= sched.total_items || item < kBailRounds * static_cast<int>(gridDim.x)) break;
             if (failed * kBailOneIn <= item) break;
             if (atomicExch(&p.redo_flags[item], 1) == 0) p.redo_list[atomicAdd(p.redo_count, 1)] = item;
