@@ -262,8 +262,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       // issued by one elected lane.
       const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
       auto wait_all = [&](uint32_t bar, uint32_t parity, int tag) -> bool {
-        const bool r = mbar_wait(bar, parity, abort_flag, wait_ns, tag);
-        return __all_sync(0xffffffffu, r) != 0;
+        return mbar_wait_warp(bar, parity, abort_flag, wait_ns, tag);
       };
       constexpr uint32_t idesc_qk = make_idesc_f16(kTileM, kTileN, kBf16, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(kTileM, D, kBf16, false, true);
@@ -465,8 +464,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
 #endif
     while (ok) {
       const int slot = item_count & 1;
-      ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait_warp(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
       if (!ok) break;
       const int item = sched_ring[slot];
       __syncwarp();
@@ -494,8 +492,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       while (j < n_tiles) {
       int careful_half = -1;     // >= 0: the half of key tile j that failed the check
       for (; j < n_tiles; ++j) {
-        ok = mbar_wait(bar_s_full(t), s_count & 1, abort_flag, wait_ns, kTagSFull);
-        ok = __all_sync(0xffffffffu, ok);
+        ok = mbar_wait_warp(bar_s_full(t), s_count & 1, abort_flag, wait_ns, kTagSFull);
         if (!ok) break;
         ++s_count;
         tc_fence_after_sync();
@@ -624,8 +621,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         if (p.causal) limit = min(limit, row - n0);
         for (int half = careful_half; half < 2; ++half) {
           if (half == 1) {
-            ok = mbar_wait(bar_pv0_done(t), (s_count - 1) & 1, abort_flag, wait_ns, kTagPvDone);
-            ok = __all_sync(0xffffffffu, ok);
+            ok = mbar_wait_warp(bar_pv0_done(t), (s_count - 1) & 1, abort_flag, wait_ns, kTagPvDone);
             if (!ok) break;
             tc_fence_after_sync();
           }
@@ -645,8 +641,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
       if (!ok) break;
 
       // ---- epilogue: O_t / l -> global, lse = m + log l
-      ok = mbar_wait(bar_o_full(t), o_count & 1, abort_flag, wait_ns, kTagOFull);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait_warp(bar_o_full(t), o_count & 1, abort_flag, wait_ns, kTagOFull);
       if (!ok) break;
       ++o_count;
       tc_fence_after_sync();

@@ -265,8 +265,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     const int t = warp - C::kMmaWarp0;
     const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
     auto wait_all = [&](uint32_t bar, uint32_t parity, int tag) -> bool {
-      const bool r = mbar_wait(bar, parity, abort_flag, wait_ns, tag);
-      return __all_sync(0xffffffffu, r) != 0;
+      return mbar_wait_warp(bar, parity, abort_flag, wait_ns, tag);
     };
     constexpr uint32_t idesc_qk = make_idesc_f16(kRowsDb, kKeysDb, kBf16, false, false);
     constexpr uint32_t idesc_pv = make_idesc_f16(kRowsDb, D, kBf16, false, true);
@@ -421,8 +420,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
 #endif
     while (ok) {
       const int slot = item_count & 1;
-      ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait_warp(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
       if (!ok) break;
       const int item = sched_ring[slot];
       __syncwarp();
@@ -448,8 +446,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         for (; j < n; ++j) {
           const int buf = j & 1;
           const uint32_t tS = tmem_base + lane_base + C::col_s(t, buf);
-          ok = mbar_wait(bar_s_full(t, buf), s_count[buf] & 1, abort_flag, wait_ns, kTagSFull);
-          ok = __all_sync(0xffffffffu, ok);
+          ok = mbar_wait_warp(bar_s_full(t, buf), s_count[buf] & 1, abort_flag, wait_ns, kTagSFull);
           if (!ok) break;
           ++s_count[buf];
           tc_fence_after_sync();
@@ -533,8 +530,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           const int buf = j & 1;
           const uint32_t tS = tmem_base + lane_base + C::col_s(t, buf);
           if (j > 0) {
-            ok = mbar_wait(bar_pv_done(t), (pv_count + j - 1) & 1, abort_flag, wait_ns, kTagOFull);
-            ok = __all_sync(0xffffffffu, ok);
+            ok = mbar_wait_warp(bar_pv_done(t), (pv_count + j - 1) & 1, abort_flag, wait_ns, kTagOFull);
             if (!ok) break;
             tc_fence_after_sync();
           }
@@ -555,8 +551,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       if constexpr (C::kEpi) {
         // ---- the epilogue warps store O: they get 1 / l; lse = m + log l is written here
         if (o_count > 0) {   // they are done with the item before (long ago, as a rule)
-          ok = mbar_wait(bar_o_free, (o_count - 1) & 1, abort_flag, wait_ns, kTagOFull);
-          ok = __all_sync(0xffffffffu, ok);
+          ok = mbar_wait_warp(bar_o_free, (o_count - 1) & 1, abort_flag, wait_ns, kTagOFull);
           if (!ok) break;
         }
         ++o_count;
@@ -568,8 +563,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       }
       if constexpr (C::kEpi) continue;
       // ---- epilogue: O_t / l -> global, lse = m + log l (natural log; :400-404)
-      ok = mbar_wait(bar_o_full(t), o_count & 1, abort_flag, wait_ns, kTagOFull);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait_warp(bar_o_full(t), o_count & 1, abort_flag, wait_ns, kTagOFull);
       if (!ok) break;
       ++o_count;
       tc_fence_after_sync();
@@ -602,8 +596,7 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
 #endif
     while (ok) {
       const int slot = item_count & 1;
-      ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait_warp(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
       if (!ok) break;
       const int item = sched_ring[slot];
       __syncwarp();
@@ -612,13 +605,11 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       int bh, row0;
       decode(item, bh, row0);
       const int b = bh / p.H, h = bh - b * p.H;
-      ok = mbar_wait(bar_epi_ready, item_count & 1, abort_flag, wait_ns, kTagOFull);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait_warp(bar_epi_ready, item_count & 1, abort_flag, wait_ns, kTagOFull);
       if (!ok) break;
       const float inv_l = s_inv_l[wq * 32 + lane];
       RSFA_TRACE_EV(0xe000);   // 1 / l seen
-      ok = mbar_wait(bar_o_full(0), item_count & 1, abort_flag, wait_ns, kTagOFull);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait_warp(bar_o_full(0), item_count & 1, abort_flag, wait_ns, kTagOFull);
       if (!ok) break;
       tc_fence_after_sync();
       RSFA_TRACE_EV(0x6000);   // O seen

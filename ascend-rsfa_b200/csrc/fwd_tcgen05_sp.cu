@@ -218,8 +218,7 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       const int t = warp - kMmaWarpSp0;
       const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
       auto wait_all = [&](uint32_t bar, uint32_t parity, int tag) -> bool {
-        const bool r = mbar_wait(bar, parity, abort_flag, wait_ns, tag);
-        return __all_sync(0xffffffffu, r) != 0;
+        return mbar_wait_warp(bar, parity, abort_flag, wait_ns, tag);
       };
       constexpr uint32_t idesc_qk = make_idesc_f16(kRows, kKeys, kBf16, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(kRows, kD, kBf16, false, true);
@@ -336,8 +335,7 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     bool ok = true;
     while (ok) {
       const int slot = item_count & 1;
-      ok = mbar_wait(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait_warp(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
       if (!ok) break;
       const int item = sched_ring[slot];
       __syncwarp();
@@ -355,8 +353,7 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       float l = 0.f;
       bool overflow = false;     // a sum check failed: this item has to be run again
       for (int j = 0; j < n_tiles; ++j) {
-        ok = mbar_wait(bar_s_full(t), s_count & 1, abort_flag, wait_ns, kTagSFull);
-        ok = __all_sync(0xffffffffu, ok);
+        ok = mbar_wait_warp(bar_s_full(t), s_count & 1, abort_flag, wait_ns, kTagSFull);
         if (!ok) break;
         ++s_count;
         tc_fence_after_sync();
@@ -443,8 +440,7 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         l += h;
         // P_t still belongs to the PV MMAs of the previous key tile until they have completed.
         if (j > 0) {
-          ok = mbar_wait(bar_p_free(t), (pf_count + j - 1) & 1, abort_flag, wait_ns, kTagPvDone);
-          ok = __all_sync(0xffffffffu, ok);
+          ok = mbar_wait_warp(bar_p_free(t), (pf_count + j - 1) & 1, abort_flag, wait_ns, kTagPvDone);
           if (!ok) break;
           tc_fence_after_sync();
         }
@@ -460,8 +456,7 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         p.redo_list[atomicAdd(p.redo_count, 1)] = item;   // first warp to mark the item also lists it
 
       // ---- epilogue: O_t / l -> global, lse = m + log l
-      ok = mbar_wait(bar_o_full(t), o_count & 1, abort_flag, wait_ns, kTagOFull);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait_warp(bar_o_full(t), o_count & 1, abort_flag, wait_ns, kTagOFull);
       if (!ok) break;
       ++o_count;
       tc_fence_after_sync();

@@ -116,6 +116,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return mbar_wait_slow(bar, parity, abort_flag, limit_ns, tag);
 }
 
+// The same for a role that all 32 lanes of a warp run together (MMA issuers, softmax and epilogue
+// warps): every lane polls, and the warp must leave the wait as one.  The first try is a single
+// instruction executed by the converged warp, so every lane sees the same answer and no vote is
+// needed when the phase has completed already - which is the usual case for the MMA warps, whose
+// waits pace the whole CTA (the vote cost them 20 to 30 clk per wait, 1.4 % of a step).  Only the
+// slow path, in which lanes loop on their own, ends in a vote.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               uint64_t limit_ns, int tag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const bool r = mbar_wait_slow(bar, parity, abort_flag, limit_ns, tag);
+  return __all_sync(0xffffffffu, r) != 0;
+}
+
 // ------------------------------------------------- programmatic dependent launch
 // A kernel launched with programmatic stream serialisation may start while the kernel in front of
 // it on the stream is still running.  griddep_wait() returns once that kernel has completed and its
