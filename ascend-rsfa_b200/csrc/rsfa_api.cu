@@ -144,7 +144,7 @@ const char* rsfa_strerror(int code) {
     case RSFA_ERR_CUDA: return "CUDA call failed";
     case RSFA_ERR_DEVICE_STATUS: return "a kernel reported a non-zero device status (bounded wait expired)";
     case RSFA_ERR_NO_DEVICE: return "no usable sm_100 CUDA device";
-    case RSFA_ERR_TOO_LARGE: return "problem exceeds the fixed scratch of the allocation-free entry point";
+    case RSFA_ERR_TOO_LARGE: return "problem too large: beyond the fixed scratch of the allocation-free entry point, or more CTAs than a grid holds";
     default: return "unknown error code";
   }
 }
@@ -377,6 +377,8 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   cudaError_t e;
   int redo_slot = -1;
   const int path = choose_path(S, D, sm_scale, static_cast<long long>(B) * H);
+  // one CTA per (head, block of 64 rows), all on grid.x, whose limit is 2^31 - 1
+  if (path == RSFA_PATH_GENERIC && rsfa::generic_grid_blocks(B, H, S) > 2147483647LL) return RSFA_ERR_TOO_LARGE;
   {
     int bm = 0, bn = 0;
     tile_of_path(path, S, D, causal, block_m, block_n, &bm, &bn);

@@ -33,7 +33,7 @@ extern "C" {
 #define RSFA_ERR_CUDA (-3)             /* a CUDA runtime / driver call failed                   */
 #define RSFA_ERR_DEVICE_STATUS (-4)    /* a kernel reported a non-zero status (bounded wait...) */
 #define RSFA_ERR_NO_DEVICE (-5)        /* no CUDA device, or not an sm_100 device               */
-#define RSFA_ERR_TOO_LARGE (-6)        /* rsfa_fwd_noalloc: problem exceeds its fixed scratch   */
+#define RSFA_ERR_TOO_LARGE (-6)        /* beyond rsfa_fwd_noalloc's fixed scratch, or > 2^31-1 CTAs */
 
 #define RSFA_DTYPE_F16 0
 #define RSFA_DTYPE_BF16 1
