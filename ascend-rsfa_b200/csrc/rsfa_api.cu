@@ -35,6 +35,8 @@ struct DeviceState {
   int* redo = nullptr;               // kRedoSlots blocks, allocated at the first D = 64 call that can use them
   cudaEvent_t redo_done[kRedoSlots] = {};   // recorded behind the last launches that used the block
   bool redo_held[kRedoSlots] = {};          // a host thread is between taking the block and recording its event
+  bool redo_used[kRedoSlots] = {};          // the block has been used at all
+  cudaStream_t redo_stream[kRedoSlots] = {};   // stream of the block's last user
   // staging buffers of rsfa_fwd_host (grow-only)
   void* stage[2][4] = {{nullptr, nullptr, nullptr, nullptr}, {nullptr, nullptr, nullptr, nullptr}};
   float* stage_lse[2] = {nullptr, nullptr};
@@ -397,9 +399,13 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
       }
       cudaSetDevice(prev);
     }
-    // A block that no host thread holds and whose last user has finished on the GPU.  None free
-    // (eight such calls still in flight on this device): this call runs the 128-key kernel alone,
-    // which needs no scratch.
+    // A block whose last user ran on this call's stream can be taken at once: stream order puts this
+    // call's memset and kernels behind that user's.  Otherwise a block that no host thread holds and
+    // whose last user has finished on the GPU (its event says so).  None free (eight such calls of other
+    // streams still in flight on this device): this call runs the 128-key kernel alone, which needs
+    // no scratch.
+    for (int i = 0; d->redo != nullptr && i < kRedoSlots && redo_slot < 0; ++i)
+      if (!d->redo_held[i] && d->redo_used[i] && d->redo_stream[i] == static_cast<cudaStream_t>(stream)) redo_slot = i;
     for (int i = 0; d->redo != nullptr && i < kRedoSlots && redo_slot < 0; ++i) {
       if (d->redo_held[i]) continue;
       if (d->redo_done[i] == nullptr &&
@@ -427,8 +433,20 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   g_launches.fetch_add(launches);
   if (redo_slot >= 0) {
     std::lock_guard<std::mutex> lock(g_mu);
-    if (cudaEventRecord(d->redo_done[redo_slot], static_cast<cudaStream_t>(stream)) != cudaSuccess) cudaGetLastError();
-    d->redo_held[redo_slot] = false;
+    if (d->redo_done[redo_slot] == nullptr &&
+        cudaEventCreateWithFlags(&d->redo_done[redo_slot], cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      d->redo_done[redo_slot] = nullptr;
+    }
+    // Without an event the block stays held for good: better one block less than one shared by two streams.
+    if (d->redo_done[redo_slot] != nullptr &&
+        cudaEventRecord(d->redo_done[redo_slot], static_cast<cudaStream_t>(stream)) == cudaSuccess) {
+      d->redo_used[redo_slot] = true;
+      d->redo_stream[redo_slot] = static_cast<cudaStream_t>(stream);
+      d->redo_held[redo_slot] = false;
+    } else {
+      cudaGetLastError();
+    }
   }
   if (e == cudaSuccess && check_status) {
     // The status word follows the kernels to the host on the same stream; the next call looks at it.
