@@ -1,6 +1,6 @@
 """Offline tile sweep for the tcgen05 kernel family on a B200.
 
-    python ascend-rsfa_b200/tile_sweep.py [--write] [--iters N]
+    python ascend-rsfa_b200/tile_sweep.py [--write] [--out FILE] [--iters N]
 
 Counterpart of the reference's tiling/search_optimal_tiling.py: for every (S, D, causal) of the
 sweep list it runs each instantiated tile — (128, 128) = single-buffered S, (128, 64) =
@@ -54,6 +54,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--write", action="store_true")
     ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--out", default=os.path.join(HERE, "csrc", "tile_table.inc"),
+                    help="where --write puts the table (default: the file the build includes)")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
     g = torch.Generator(device=dev).manual_seed(42)
@@ -102,9 +104,9 @@ def main():
                     lines.append("{%d, %d, %d, %d, %d, %d},\n" % (lo, hi - 1, D, causal, bm, bn))
         for causal in (0, 1):
             lines.append("{129, 1 << 30, 256, %d, 128, 64},\n" % causal)
-        with open(os.path.join(HERE, "csrc", "tile_table.inc"), "w") as f:
+        with open(args.out, "w") as f:
             f.writelines(lines)
-        print("wrote csrc/tile_table.inc; rebuild with build.py")
+        print("wrote %s; rebuild with build.py" % args.out)
 
 
 if __name__ == "__main__":

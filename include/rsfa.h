@@ -94,7 +94,7 @@ RSFA_API int rsfa_fwd_host(const void* q_host, const void* k_host, const void* v
  * process exits) and calls no cudaMalloc, cudaFree or other allocating routine.
  *
  * Arguments as rsfa_fwd, without block_m / block_n: the tile table decides, so either tcgen05
- * kernel family may run (64-key tiles at D = 256 and for D = 128 causal around S = 1024, 128-key
+ * kernel family may run (64-key tiles at D = 256 and for short causal sequences, 128-key
  * tiles otherwise; the D = 64 separate-P kernel, whose redo list is allocated scratch, is not used).
  * Every in-kernel wait is bounded by the "wait_limit_ms" option, as in rsfa_fwd.  Limits: only
  * shapes the tcgen05 kernels are built for (sm_scale > 0; D = 16 and 32 run on the D = 64 kernel) -> otherwise

@@ -115,7 +115,8 @@ o = torch.empty_like(q)
 st = (ctypes.c_int64 * 16)(*(list(q.stride()) * 4))
 stream = torch.cuda.current_stream().cuda_stream
 def call():
-    rc = lib.rsfa_fwd_noalloc(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), None, B, H, S, D, st, 1, 0.25,
+    # non-causal: the tile table sends this shape to the 128-key kernel, the one with the test hook used below
+    rc = lib.rsfa_fwd_noalloc(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), None, B, H, S, D, st, 0, 0.25,
                               _capi.RSFA_DTYPE_F16, stream)
     assert rc == 0, _capi.strerror(rc)
     torch.cuda.synchronize()
@@ -142,7 +143,7 @@ assert rc == _capi.RSFA_ERR_DEVICE_STATUS and (raw.value >> 16) == 1, (rc, hex(r
 ref = torch.empty_like(q)
 call()                                   # and the next call is whole again
 o_after = o.clone()
-rc = lib.rsfa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), ref.data_ptr(), None, B, H, S, D, st, 1, 0.25, 128, 128,
+rc = lib.rsfa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), ref.data_ptr(), None, B, H, S, D, st, 0, 0.25, 128, 128,
                   _capi.RSFA_DTYPE_F16, stream)
 torch.cuda.synchronize()
 assert rc == 0 and torch.equal(o_after, ref)
