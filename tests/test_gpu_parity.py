@@ -477,6 +477,41 @@ def test_size_independent_properties_at_full_cfg2_heads(fa, cuda_device):
     fa.device_status()
 
 
+@pytest.mark.parametrize("name", ["cfg2", "cfg3", "cfg4", "cfg5"])
+def test_full_size_configurations_through_size_independent_properties(fa, cuda_device, name):
+    """Every benchmark configuration at its FULL size (all B x H heads in one launch, so every work item of
+    the queue, the last partly filled wave included): with V = 1 every output element is the sum of a
+    row of P and must be 1, whatever Q and K are; the log-sum-exp must be finite everywhere; and the two
+    kernel families ((128,128) and (128,64) tiles, where both exist) must agree on random V within the
+    tolerance.  The oracle cannot follow to these sizes; it checks the per-head shapes in the tests above."""
+    B, H, S, D, scale, mult = CONFIGS[name]
+    dev = cuda_device
+    g = torch.Generator(device=dev).manual_seed(11)
+    q = (torch.randn(B, H, S, D, generator=g, device=dev) * mult).half()
+    k = (torch.randn(B, H, S, D, generator=g, device=dev) * mult).half()
+    ones = torch.ones(B, H, S, D, dtype=torch.float16, device=dev)
+    for causal in (False, True):
+        bm, bn = fa.get_tiling(B, H, S, D, causal)
+        o, lse = fa.attention_with_lse(q, k, ones, causal, scale, bm, bn)
+        torch.cuda.synchronize()
+        assert float((o.float() - 1.0).abs().max()) < 2e-3, (name, causal)
+        assert bool(torch.isfinite(lse).all())
+        del o, lse
+    del ones
+    v = (torch.randn(B, H, S, D, generator=g, device=dev) * mult).half()
+    if D <= 128:
+        for causal in (False, True):
+            a = fa.attention(q, k, v, causal, scale, 128, 128)
+            b = fa.attention(q, k, v, causal, scale, 128, 64)
+            torch.cuda.synchronize()
+            diff = (a.float() - b.float()).abs()
+            assert bool((diff <= ATOL + RTOL * b.float().abs()).all()), (name, causal, float(diff.max()))
+            del a, b, diff
+    fa.device_status()
+    del q, k, v
+    torch.cuda.empty_cache()
+
+
 def test_host_buffer_entry_point(fa, cuda_device):
     q, k, v = make_inputs(3, 5, 384, 64, seed=6)
     fa.set_option("host_slab_heads", 4)   # 15 heads -> slabs of 4,4,4,3: exercises the double buffer
