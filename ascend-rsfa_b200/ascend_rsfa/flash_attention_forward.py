@@ -36,6 +36,31 @@ _lib = _capi.load()
 DEVICE = "cuda"
 _DTYPES = {torch.float16: _capi.RSFA_DTYPE_F16, torch.bfloat16: _capi.RSFA_DTYPE_BF16}
 
+# The raw handle of the current stream without building a torch.cuda.Stream object (3 us per call,
+# a tenth of a short-sequence call); the public route is the fallback.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _current_stream(index):
+    if _raw_stream is not None:
+        return _raw_stream(index)
+    return torch.cuda.current_stream(index).cuda_stream
+
+
+# ctypes stride arrays of dense [B, H, S, D] problems, by shape: building one costs 2 us
+_dense_strides = {}
+
+
+def _strides_of(qd, kd, vd, o):
+    if qd.is_contiguous() and kd.is_contiguous() and vd.is_contiguous() and o.is_contiguous():
+        arr = _dense_strides.get(qd.shape)
+        if arr is None:
+            if len(_dense_strides) > 256:
+                _dense_strides.clear()
+            arr = _dense_strides[qd.shape] = (ctypes.c_int64 * 16)(*(tuple(o.stride()) * 4))
+        return arr
+    return (ctypes.c_int64 * 16)(*qd.stride(), *kd.stride(), *vd.stride(), *o.stride())
+
 
 def get_num_compute_cores():
     """SM count of the current CUDA device (the reference returns the AI-core count, :19-21)."""
@@ -76,16 +101,16 @@ def _forward(q, k, v, causal, sm_scale, BM, BN, want_lse):
     if not (o.stride(-1) == 1 and all(o.shape[i] == 1 or o.stride(i) % 8 == 0 for i in range(3))):
         o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     M = torch.empty((Z, H, N_CTX), dtype=torch.float32, device=q.device) if want_lse else None
-    strides = (ctypes.c_int64 * 16)(*qd.stride(), *kd.stride(), *vd.stride(), *o.stride())
+    strides = _strides_of(qd, kd, vd, o)
     args = (qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), M.data_ptr() if M is not None else None,
             Z, H, N_CTX, HEAD_DIM, strides, 1 if causal else 0, float(sm_scale), int(BM), int(BN),
             _DTYPES[q.dtype])
     # rsfa_fwd launches on the CURRENT device; switching costs microseconds, so only when needed
     if q.device.index == torch.cuda.current_device():
-        rc = _lib.rsfa_fwd(*args, torch.cuda.current_stream().cuda_stream)
+        rc = _lib.rsfa_fwd(*args, _current_stream(q.device.index))
     else:
         with torch.cuda.device(q.device):
-            rc = _lib.rsfa_fwd(*args, torch.cuda.current_stream().cuda_stream)
+            rc = _lib.rsfa_fwd(*args, _current_stream(q.device.index))
     if rc != 0:
         _capi.check(rc, "rsfa_fwd")
     return o, M

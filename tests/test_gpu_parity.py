@@ -58,8 +58,8 @@ def test_cfg1(fa, cuda_device, causal):
     assert m["max_abs"] < 4e-3
 
 
-# The reference's own test shapes (flash_attention_forward.py:671-699), N(0, 0.5), sm_scale 0.5,
-# with batch reduced where the oracle would take too long.
+# The reference's own fp16 test shapes (flash_attention_forward.py:671-697; the bf16 one is in test_bf16),
+# N(0, 0.5), sm_scale 0.5, with batch reduced where the oracle would take too long.
 REFERENCE_SHAPES = [
     (1, 2, 1024, 64, False, 64, 32), (1, 1, 64, 64, False, 64, 16), (4, 32, 64, 64, False, 64, 32),
     (1, 1, 128, 128, False, 16, 16), (1, 1, 128, 128, False, 64, 64), (4, 32, 128, 128, False, 32, 64),
@@ -68,7 +68,7 @@ REFERENCE_SHAPES = [
     (1, 1, 128, 128, True, 32, 32), (1, 2, 1024, 64, True, 128, 32), (2, 4, 2048, 128, False, 128, 128),
     (2, 4, 4096, 64, False, 128, 128), (4, 8, 1024, 128, False, 128, 128), (4, 8, 1024, 64, False, 128, 128),
     (2, 4, 2048, 64, True, 64, 64), (4, 8, 1024, 64, True, 64, 64), (4, 32, 512, 64, True, 64, 64),
-    (4, 32, 256, 128, True, 64, 64),
+    (4, 32, 256, 128, True, 64, 64), (4, 32, 64, 64, False, 64, 16), (4, 32, 64, 64, True, 64, 16),
 ]
 
 
@@ -80,7 +80,8 @@ def test_reference_test_shapes(fa, cuda_device, Z, H, N, D, causal, BM, BN):
 
 
 def test_bf16(fa, cuda_device):
-    q, k, v = make_inputs(2, 4, 1024, 64, seed=20, std=0.5, dtype=torch.bfloat16)
+    # the reference's one bf16 case is (128, 8, 1024, 64), non-causal, tile (128, 128) (:698); 16 of its heads here
+    q, k, v = make_inputs(2, 8, 1024, 64, seed=20, std=0.5, dtype=torch.bfloat16)
     check(fa, q, k, v, False, 0.5, 128, 128, cuda_device, tol=2e-2)
     q, k, v = make_inputs(1, 2, 512, 128, seed=21, std=0.5, dtype=torch.bfloat16)
     check(fa, q, k, v, True, 0.5, 128, 128, cuda_device, tol=2e-2)
