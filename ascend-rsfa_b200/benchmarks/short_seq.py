@@ -6,7 +6,7 @@ A call on S <= 128 is one key tile per query tile: it reads Q, K, V once and wri
 (4 * B * H * S * D * 2 bytes) and does next to no arithmetic, so HBM bandwidth bounds it - for the
 large batches; the small ones (the reference's single-tile kernels _attn_fwd_small /
 _attn_fwd_small_causal, ascend_rsfa/flash_attention_forward.py:26-159, serve 2 to 128 heads in its
-tests, :673-677) are bound by the latency of one launch.  The inputs of successive calls rotate
+tests, :673-677) are bound by the latency of one call.  The inputs of successive calls rotate
 through a pool larger than the 126 MB L2, so every call reads from DRAM.
 
 bench.py imports measure() for its `short_seq` record; run standalone (one shape, few iterations)
@@ -56,8 +56,7 @@ def measure(fa, dev, hbm_gbs, shape, causal=False, sm_scale=0.5, iters=400, chec
     ev1.record()
     torch.cuda.synchronize()
     us = ev0.elapsed_time(ev1) / iters * 1e3
-    # the tcgen05 kernels take 256 query rows per work item, the short-sequence kernel 64
-    tc = S > 64 and fa.work_items(B, H, S, D, causal, sm_scale) == B * H
+    tc = fa.select_path(S, D, causal, sm_scale, bm, bn)[0] == 1
     rec = {"shape": [B, H, S, D], "causal": bool(causal), "us_per_call": us, "bytes_per_call": nbytes,
            "gb_per_s": nbytes / (us * 1e-6) / 1e9,
            "frac_of_measured_hbm": (nbytes / (us * 1e-6) / 1e9 / hbm_gbs) if hbm_gbs else None,

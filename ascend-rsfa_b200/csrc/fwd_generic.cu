@@ -1,11 +1,14 @@
 // Generic FlashAttention-2 forward for sm_100a on the legacy tensor path
-// (mma.sync m16n8k16, fp32 accumulate).  It is the short-sequence path — the
-// counterpart of the reference's single-tile kernels _attn_fwd_small and
-// _attn_fwd_small_causal (ascend_rsfa/flash_attention_forward.py:26-159), which
-// are latency- and HBM-bound — and it also serves every shape the tcgen05 kernel
-// is not instantiated for (D = 16, 32; non-positive sm_scale).  Any S >= 1, any
-// strides with a contiguous innermost dimension; rows and keys past S are
-// predicated, which the reference does not do.
+// (mma.sync m16n8k16, fp32 accumulate): the counterpart of the reference's
+// single-tile kernels _attn_fwd_small and _attn_fwd_small_causal
+// (ascend_rsfa/flash_attention_forward.py:26-159), which are latency- and
+// HBM-bound.  The dispatcher sends it the smallest tiles - head dimension 16 at
+// S <= 128, sequences of at most 64 keys at D <= 64 - where it measures faster
+// than the tcgen05 kernels, and every shape with a non-positive sm_scale, which
+// those are not built for.  It accepts any S >= 1, any D in {16,32,64,128,256} and
+// any strides with a contiguous innermost dimension (the "force_path" option runs
+// it on every shape: the parity tests compare the two families that way); rows and
+// keys past S are predicated, which the reference does not do.
 //
 // One CTA = 4 warps = 64 query rows; each warp owns 16 rows and sweeps the keys
 // in tiles of kBN with the online-softmax recurrence of _attn_fwd_inner

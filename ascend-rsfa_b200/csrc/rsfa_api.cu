@@ -94,22 +94,25 @@ int ensure_device(int device, DeviceState** out) {
 
 bool valid_head_dim(int D) { return D == 16 || D == 32 || D == 64 || D == 128 || D == 256; }
 
-// Kernel family by shape.  Sequences of at most 128 keys are a single tile: small batches of them
-// go to the short-sequence kernel, like the reference's N_CTX <= 128 rule (:564) - it starts faster
-// (26 against 28 to 33 us per call at a handful of heads).  From kShortSeqHeads heads on, the
-// tcgen05 kernel takes them too where it is instantiated: it runs such batches at the HBM rate
-// (512 x 8 heads of S = 128, D = 128: 87 us = 6.2 TB/s against 304 us), the mma.sync kernel does
-// not; only S <= 64 at D <= 64 (72 against 85 us at D = 64) and D = 16 (56 against 68 us at S = 128)
-// stay.  Longer sequences go to the tcgen05 kernel where it is instantiated.
-constexpr long long kShortSeqHeads = 256;
-int choose_path(int S, int D, float sm_scale, long long heads) {
+// Kernel family by shape.  The tcgen05 kernels take everything they are instantiated for (sm_scale > 0)
+// except the smallest tiles: head dimension 16, and sequences of at most 64 keys at D <= 64, stay on
+// the short-sequence kernel, the counterpart of the reference's single-tile kernels for N_CTX <= 128
+// (:564).  Measured per call, host clock around call + synchronise / 4096 heads back to back:
+//   S = 128 D = 128: 34 against 44 us at 128 heads, 93 against 346 us at 4096 (HBM rate against not);
+//   S = 128 D = 64: 33 against 41 us; D = 256: 34 against 52 us; S = 128 D = 32: 66 against 107 us at 4096;
+//   S = 64 D = 64: 32 against 34 us at 128 heads but 78 against 74 us at 4096; S = 64 D = 32: 77 against 38 us;
+//   D = 16: 66 against 59 us at 4096 heads, 32 against 29 us at 2.
+// The batch size does not enter: since a launch sets itself up under the tail of the one before, claims
+// its first work item without the queue and needs no memset, the tcgen05 kernel starts as fast as
+// the small one.
+int choose_path(int S, int D, float sm_scale) {
   const long long forced = g_force_path.load();
   const bool tc_ok = rsfa::tcgen05_supports(S, D, sm_scale);
   if (forced == RSFA_PATH_GENERIC) return RSFA_PATH_GENERIC;
   if (forced == RSFA_PATH_TCGEN05 && tc_ok) return RSFA_PATH_TCGEN05;
   if (!tc_ok) return RSFA_PATH_GENERIC;
   if (S > 128) return RSFA_PATH_TCGEN05;
-  return (heads >= kShortSeqHeads && D >= 32 && !(S <= 64 && D <= 64)) ? RSFA_PATH_TCGEN05 : RSFA_PATH_GENERIC;
+  return (D >= 32 && !(S <= 64 && D <= 64)) ? RSFA_PATH_TCGEN05 : RSFA_PATH_GENERIC;
 }
 
 // Tile a call runs: on the tcgen05 path the request is honoured when instantiated, otherwise the
@@ -232,7 +235,7 @@ int rsfa_select_path(int S, int D, int causal, float sm_scale, int block_m, int 
   if (path == nullptr || S < 1 || !valid_head_dim(D) || block_m < 1 || block_n < 1 ||
       (dtype != RSFA_DTYPE_F16 && dtype != RSFA_DTYPE_BF16))
     return RSFA_ERR_INVALID_ARGUMENT;
-  *path = choose_path(S, D, sm_scale, 1);   // no batch here: the answer for a small batch
+  *path = choose_path(S, D, sm_scale);
   int bm, bn;
   tile_of_path(*path, S, D, causal, block_m, block_n, &bm, &bn);
   if (tile_m != nullptr) *tile_m = bm;
@@ -243,9 +246,9 @@ int rsfa_select_path(int S, int D, int causal, float sm_scale, int block_m, int 
 int rsfa_get_tiling(int B, int H, int S, int D, int causal, int* block_m, int* block_n) {
   if (block_m == nullptr || block_n == nullptr || B < 1 || H < 1 || S < 1 || !valid_head_dim(D))
     return RSFA_ERR_INVALID_ARGUMENT;
-  // The table: one row per (S bucket, D); the causal flag does not change the tile because the
-  // diagonal is handled by a masked variant of the same tile.  sm_scale is taken as positive here.
-  const int path = (rsfa::tcgen05_supports(S, D, 1.0f) && S > 128) ? RSFA_PATH_TCGEN05 : RSFA_PATH_GENERIC;
+  // The tile of the kernel family the shape runs on (sm_scale is taken as positive here): a row of
+  // the tile table on the tcgen05 path, the short-sequence kernel's single tile otherwise.
+  const int path = choose_path(S, D, 1.0f);
   tile_of_path(path, S, D, causal, 0, 0, block_m, block_n);
   return RSFA_OK;
 }
@@ -253,7 +256,7 @@ int rsfa_get_tiling(int B, int H, int S, int D, int causal, int* block_m, int* b
 int rsfa_work_items(int B, int H, int S, int D, int causal, float sm_scale, long long* items) {
   if (items == nullptr || B < 1 || H < 1 || S < 1 || !valid_head_dim(D)) return RSFA_ERR_INVALID_ARGUMENT;
   const long long heads = static_cast<long long>(B) * H;
-  if (choose_path(S, D, sm_scale, heads) == RSFA_PATH_GENERIC) {
+  if (choose_path(S, D, sm_scale) == RSFA_PATH_GENERIC) {
     *items = rsfa::generic_grid_blocks(B, H, S);
   } else {
     const int rows = (D == 256) ? 128 : 256;   // query rows per work item of the tcgen05 kernels
@@ -378,7 +381,7 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   long long launches = 0;
   cudaError_t e;
   int redo_slot = -1;
-  const int path = choose_path(S, D, sm_scale, static_cast<long long>(B) * H);
+  const int path = choose_path(S, D, sm_scale);
   // one CTA per (head, block of 64 rows), all on grid.x, whose limit is 2^31 - 1
   if (path == RSFA_PATH_GENERIC && rsfa::generic_grid_blocks(B, H, S) > 2147483647LL) return RSFA_ERR_TOO_LARGE;
   {

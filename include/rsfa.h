@@ -39,7 +39,7 @@ extern "C" {
 #define RSFA_DTYPE_BF16 1
 
 /* Kernel families a call can be routed to (see rsfa_select_path). */
-#define RSFA_PATH_GENERIC 0 /* mma.sync kernel: any S, D in {16,32,64,128,256}; the short-sequence path */
+#define RSFA_PATH_GENERIC 0 /* mma.sync kernel: any S, D in {16,32,64,128,256}; the smallest tiles, scale <= 0 */
 #define RSFA_PATH_TCGEN05 1 /* warp-specialised tcgen05 / TMEM / TMA kernel                         */
 
 /*
@@ -124,9 +124,9 @@ RSFA_API int rsfa_get_tiling(int B, int H, int S, int D, int causal, int* block_
 /*
  * Which kernel family rsfa_fwd would use for this problem, and the tile it would run
  * (after snapping block_m/block_n).  Counterpart of the dispatch in _attention.forward (:564-610).
- * tile_m / tile_n may be NULL.  The call carries no batch size: for S <= 128 it answers for a
- * small batch (the short-sequence kernel); rsfa_fwd sends batches of 256 heads or more of such
- * sequences to the tcgen05 kernel where that is instantiated (except S <= 64 at D <= 64, and D = 16).
+ * tile_m / tile_n may be NULL.  The tcgen05 kernels run every shape with sm_scale > 0 except head
+ * dimension 16 at S <= 128 and sequences of at most 64 keys at D <= 64, which the short-sequence
+ * kernel serves (measured per call; the batch size does not enter).
  */
 RSFA_API int rsfa_select_path(int S, int D, int causal, float sm_scale, int block_m, int block_n, int dtype,
                      int* path, int* tile_m, int* tile_n);

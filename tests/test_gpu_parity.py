@@ -151,17 +151,22 @@ def test_both_tcgen05_variants(fa, cuda_device, variant, causal):
 
 
 @pytest.mark.parametrize("causal", [False, True])
-def test_large_batches_of_short_sequences_take_the_tcgen05_kernel(fa, cuda_device, causal):
-    # From 256 heads on, sequences of at most 128 keys run on the tcgen05 kernel (HBM-bound there);
-    # one work item is then a single, partly empty pair of Q tiles.  The launch counter shows
-    # one launch either way (a single key tile does not use the D = 64 two-launch scheme).
+def test_short_sequences_on_both_kernel_families(fa, cuda_device, causal):
+    # Sequences of at most 128 keys run on the tcgen05 kernel, whatever the batch (one work item is a
+    # single, partly empty pair of Q tiles; HBM-bound for large batches), except D = 16 and S <= 64 at
+    # D <= 64, which stay on the short-sequence kernel.  The launch counter shows one launch either
+    # way (a single key tile does not use the D = 64 two-launch scheme).
     for B, H, S, D, scale in [(40, 8, 128, 128, 0.3), (33, 8, 96, 64, 0.25), (32, 8, 128, 256, 0.0625),
                               (64, 4, 77, 128, 0.3), (64, 4, 64, 64, 0.25), (2, 4, 128, 128, 0.3),
-                              (64, 4, 128, 32, 0.3), (33, 8, 100, 16, 0.5), (64, 4, 64, 32, 0.3)]:
+                              (64, 4, 128, 32, 0.3), (33, 8, 100, 16, 0.5), (64, 4, 64, 32, 0.3), (1, 1, 128, 128, 0.3),
+                              (1, 2, 17, 256, 0.3), (1, 3, 65, 64, 0.3)]:
         q, k, v = make_inputs(B, H, S, D, seed=S + D + B)
         n0 = fa.launch_count()
         check(fa, q, k, v, causal, scale, 128, 128, cuda_device)
         assert fa.launch_count() - n0 == 1, (B, H, S, D)
+        on_tcgen05 = D >= 32 and not (S <= 64 and D <= 64)
+        assert fa.select_path(S, D, causal, scale)[0] == (1 if on_tcgen05 else 0)
+        assert fa.work_items(B, H, S, D, causal, scale) == B * H * (1 if on_tcgen05 else -(-S // 64))
 
 
 def test_separate_p_kernel_marks_items_and_they_are_run_again(fa, cuda_device):

@@ -43,11 +43,17 @@ def test_get_tiling_rejects_impossible_shapes():
 
 
 def test_path_selection_follows_the_short_sequence_rule():
-    assert fa.select_path(128, 64, False, 0.5)[0] == _capi.RSFA_PATH_GENERIC     # N_CTX <= 128 (:564)
+    # one key tile (the reference's N_CTX <= 128 rule, :564): the tcgen05 kernel takes it too, except the
+    # smallest tiles (D = 16; S <= 64 at D <= 64), which stay on the short-sequence kernel
+    assert fa.select_path(128, 64, False, 0.5) == (_capi.RSFA_PATH_TCGEN05, 128, 128)
+    assert fa.select_path(64, 64, False, 0.5)[0] == _capi.RSFA_PATH_GENERIC
+    assert fa.select_path(128, 16, True, 0.5)[0] == _capi.RSFA_PATH_GENERIC
+    assert fa.select_path(64, 128, True, 0.5)[0] == _capi.RSFA_PATH_TCGEN05
     assert fa.select_path(2048, 128, True, 0.5)[0] == _capi.RSFA_PATH_TCGEN05
     assert fa.select_path(8192, 64, False, 0.125)[0] == _capi.RSFA_PATH_TCGEN05
     assert fa.select_path(2048, 32, False, 0.5)[0] == _capi.RSFA_PATH_TCGEN05    # D = 32: the D = 64 kernel
-    assert fa.select_path(128, 32, False, 0.5)[0] == _capi.RSFA_PATH_GENERIC
+    assert fa.select_path(128, 32, False, 0.5)[0] == _capi.RSFA_PATH_TCGEN05
+    assert fa.select_path(64, 32, False, 0.5)[0] == _capi.RSFA_PATH_GENERIC
     assert fa.select_path(2048, 128, False, -0.5)[0] == _capi.RSFA_PATH_GENERIC  # non-positive scale
     assert fa.select_path(2048, 128, False, 0.5) == (1, 128, 128)
     # an instantiated tile is honoured, anything else is replaced by the table's row
@@ -133,9 +139,12 @@ def test_tile_table_is_total_and_consistent():
                 assert fa.select_path(S, D, causal, 0.1, bm, bn) == (1, bm, bn)
     for D in (16, 32):
         assert fa.get_tiling(1, 1, 4096, D, True) == fa.get_tiling(1, 1, 4096, 64, True)   # the D = 64 kernels' tiles
-        assert fa.get_tiling(1, 1, 100, D, True) == (64, 64)                              # short-sequence path
+        assert fa.get_tiling(1, 1, 60, D, True) == (64, 64)                               # short-sequence kernel
     for S in (1, 64, 128):
-        assert fa.get_tiling(1, 1, S, 128, False) == (64, 64)      # short-sequence path
+        assert fa.get_tiling(1, 1, S, 128, False) == (128, 128)    # one key tile on the tcgen05 kernel
+        assert fa.get_tiling(1, 1, S, 256, True) == (128, 64)
+    assert fa.get_tiling(1, 1, 64, 64, False) == (64, 64)          # short-sequence kernel
+    assert fa.get_tiling(1, 1, 128, 16, False) == (64, 64)
 
 
 def test_work_items_need_no_device_and_count_every_head():
@@ -148,7 +157,9 @@ def test_work_items_need_no_device_and_count_every_head():
     # short-sequence kernel: one CTA per 64 rows, all on grid.x - more heads than gridDim.y could hold
     assert f(8192, 16, 64, 64, 0, 0.5, ctypes.byref(items)) == 0 and items.value == 131072
     assert f(70000, 1, 100, 16, 1, 0.5, ctypes.byref(items)) == 0 and items.value == 140000
-    assert f(1, 2, 128, 64, 0, 0.5, ctypes.byref(items)) == 0 and items.value == 4
+    assert f(1, 2, 128, 64, 0, 0.5, ctypes.byref(items)) == 0 and items.value == 2      # tcgen05: one item per head
+    assert f(1, 2, 64, 64, 0, 0.5, ctypes.byref(items)) == 0 and items.value == 2
+    assert f(1, 2, 128, 16, 0, 0.5, ctypes.byref(items)) == 0 and items.value == 4      # short-sequence: 64 rows per CTA
     assert f(1, 1, 0, 64, 0, 0.5, ctypes.byref(items)) == _capi.RSFA_ERR_INVALID_ARGUMENT
     assert f(1, 1, 64, 64, 0, 0.5, None) == _capi.RSFA_ERR_INVALID_ARGUMENT
 
