@@ -48,9 +48,9 @@ import torch
 METRIC = "attention fwd TFLOP/s (whole job; causal FLOPs counted as half)"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the 128-key tcgen05 kernel per
 # (batch, head) of S=2048, D=128, from the ncu capture summarised in the file below (128 heads of the shape:
-# 201.4 MB read + 48.3 MB written); traffic is proportional to the number of heads (Q, K, V read once, O
+# 201.4 MB read + 48.1 MB written); traffic is proportional to the number of heads (Q, K, V read once, O
 # written once; the re-reads of K/V are served by L2).
-NCU_DRAM_BYTES_PER_HEAD_S2048_D128 = 249.7e6 / 128
+NCU_DRAM_BYTES_PER_HEAD_S2048_D128 = 249.5e6 / 128
 NCU_TRAFFIC_SOURCE = "profiles/fwd_tcgen05_d128_s2048_ncu_full.md"
 # Peaks used only when MEASURED_PEAKS.json is absent: cuBLAS bf16 burst / sustained TFLOP/s and copy GB/s.
 FALLBACK_PEAKS = {"burst": 1590.0, "sustained": 1400.0, "hbm_gbs": 6650.0}
