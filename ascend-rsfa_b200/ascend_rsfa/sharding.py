@@ -46,3 +46,28 @@ def gather_heads(local, total_heads, group=None):
         parts.append(bufs[r][:, : hi - lo])
     assert head_slab(total_heads, rank, world)[1] - head_slab(total_heads, rank, world)[0] == n
     return torch.cat(parts, dim=1)
+
+
+def slab_checksums(x):
+    """Two 64-bit checksums of a 16-bit tensor that are exact and do not depend on the order of
+    summation: the bit patterns as integers, plain and weighted by position (mod 2^64)."""
+    bits = x.contiguous().view(torch.int16).reshape(-1).long()
+    w = torch.arange(bits.numel(), device=x.device, dtype=torch.int64) % 8191 + 1
+    return torch.stack([bits.sum(), (bits * w).sum()])
+
+
+def gathered_matches_slabs(gathered, local, total_heads, group=None):
+    """After gather_heads: does every rank's slab of the assembled [1, total_heads, S, D] tensor carry the
+    checksums its owner computed on its own output?  One small all-gather; True on every rank or on none
+    only if the caller reduces the answer itself."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    mine = slab_checksums(local)
+    sums = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(sums, mine, group=group)
+    ok = gathered.shape[1] == total_heads
+    for r in range(world):
+        lo, hi = head_slab(total_heads, r, world)
+        ok = ok and bool(torch.equal(slab_checksums(gathered[:, lo:hi]), sums[r]))
+    return ok

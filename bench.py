@@ -363,19 +363,7 @@ def main():
         gathered = sharding.gather_heads(o_local, heads)
         torch.cuda.synchronize()
         gather_s = time.perf_counter() - t0
-        def checksums(x):
-            # exact and independent of the order of summation: the fp16 bit patterns as integers, plain and
-            # weighted by position (mod 2^64)
-            bits = x.contiguous().view(torch.int16).reshape(-1).long()
-            w = torch.arange(bits.numel(), device=x.device, dtype=torch.int64) % 8191 + 1
-            return torch.stack([bits.sum(), (bits * w).sum()])
-        mine = checksums(o_local)
-        sums = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(sums, mine)
-        ok = gathered.shape[1] == heads
-        for r in range(world):
-            lo_r, hi_r = sharding.head_slab(heads, r, world)
-            ok = ok and bool(torch.equal(checksums(gathered[:, lo_r:hi_r]), sums[r]))
+        ok = sharding.gathered_matches_slabs(gathered, o_local, heads)
         par["gather"] = {"ok": reduce_min(1.0 if ok else 0.0) > 0.5, "collective": "ncclAllGather of the O slabs",
                          "bytes": int(gathered.numel() * 2), "seconds": gather_s, "in_timed_region": False}
         par["ok"] = par["ok"] and par["gather"]["ok"]
