@@ -62,6 +62,14 @@ extern "C" {
  *   stream       a cudaStream_t (NULL = default stream).  The call is asynchronous like the
  *                reference's kernel launches; it does not synchronise.
  *
+ * Concurrency: calls on different streams of one device may overlap on the GPU.  Every launch takes a
+ * work queue of its own out of 1024 per device (the kernel puts it back to zero when it ends).  At
+ * D <= 64 with 128-key tiles a call is two launches that share a scratch block, one of eight per
+ * device: a call reuses the block it used last on the same stream, takes another one only when the
+ * event recorded behind that block's last user has completed, and runs the single-launch 128-key
+ * kernel when none is free (more than eight such calls of different streams in flight).  The status
+ * word is shared per device.
+ *
  * Errors: D outside {16,32,64,128,256} or mismatched (the reference asserts, :551-554), B/H/S < 1,
  * misaligned pointers or strides -> RSFA_ERR_INVALID_ARGUMENT.  A device status left by an earlier
  * launch on the same device is reported by rsfa_device_status, not here.
