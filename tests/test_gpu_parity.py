@@ -424,6 +424,41 @@ def test_d64_calls_on_several_streams_do_not_share_redo_scratch(fa, cuda_device)
         assert m["finite"] and m["allclose"], m
 
 
+def test_back_to_back_launches_of_mixed_shapes_on_two_streams(fa, cuda_device):
+    """Sixty calls of different shapes, masks and kernel families issued without a synchronisation in
+    between, alternating between two streams: every launch takes a work queue that the launch using it
+    before must have left at zero, sets itself up under the tail of the launch in front of it on its
+    stream (programmatic dependent launch) and must not touch memory before that launch is complete.
+    All outputs are compared with the oracle at the end."""
+    shapes = [(2, 3, 512, 128, 0.3), (1, 2, 300, 64, 0.25), (1, 2, 384, 256, 0.0625), (3, 4, 128, 128, 0.3),
+              (2, 2, 64, 64, 0.5), (1, 5, 1024, 128, 0.2), (2, 2, 777, 64, 0.125), (1, 1, 130, 32, 0.3)]
+    cases = []
+    for i, (B, H, S, D, scale) in enumerate(shapes):
+        q, k, v = make_inputs(B, H, S, D, seed=100 + i)
+        for causal in (False, True):
+            cases.append((q, k, v, causal, scale, attention_fp32(q, k, v, causal, scale)))
+    dev = cuda_device
+    on_dev = [tuple(t.to(dev) for t in c[:3]) for c in cases]
+    streams = [torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)]
+    torch.cuda.synchronize()
+    outs = []
+    for rep in range(4):
+        for i, (c, d) in enumerate(zip(cases, on_dev)):
+            if rep > 0 and i % 4 != rep:        # 16 + 3 x 4 = 28 calls per ... keep the total near sixty
+                continue
+            with torch.cuda.stream(streams[(i + rep) & 1]):
+                outs.append((i, fa.attention(d[0], d[1], d[2], c[3], c[4], 128, 128)))
+    for i, (c, d) in enumerate(zip(cases, on_dev)):  # and once more, all on one stream, back to back
+        with torch.cuda.stream(streams[0]):
+            outs.append((i, fa.attention(d[0], d[1], d[2], c[3], c[4], 128, 128)))
+    torch.cuda.synchronize()
+    fa.device_status()
+    assert len(outs) >= 40
+    for i, o in outs:
+        m = error_metrics(o, cases[i][5])
+        assert m["finite"] and m["allclose"], (i, m)
+
+
 def test_strided_inputs_and_views(fa, cuda_device):
     B, H, S, D = 2, 3, 256, 64
     big = torch.randn(B, S, 3, H, D, generator=torch.Generator().manual_seed(1)).half()
