@@ -372,6 +372,29 @@ def main():
 
     extras = not args.no_extras
     sustained = None
+    # ------------------------------------------------------------------ operator timing, the reference harness's way
+    # One attention() call (output allocation included) followed by a device synchronize, host clock around
+    # the pair, as benchmarks/run_final_benchmark.py:111-126 of the reference times its operator (it reports the mean).
+    operator = None
+    if extras:
+        time.sleep(IDLE_BEFORE_TIMING_S)
+        for _ in range(3):
+            fa.attention(q, k, v, main_causal, scale, bm, bn)
+        torch.cuda.synchronize()
+        barrier()
+        per_call = []
+        for _ in range(10):
+            t0 = time.perf_counter()
+            fa.attention(q, k, v, main_causal, scale, bm, bn)
+            torch.cuda.synchronize()
+            per_call.append(time.perf_counter() - t0)
+        barrier()
+        call_s = reduce_max(sorted(per_call)[len(per_call) // 2])
+        mean_s = reduce_max(sum(per_call) / len(per_call))
+        operator = {"ms_per_call": call_s * 1e3, "tflops": flops / call_s / 1e12, "calls": 10,
+                    "mean_ms_per_call": mean_s * 1e3,
+                    "note": "median of attention() + torch.cuda.synchronize() per call on the host clock, output "
+                            "allocation inside, max over ranks"}
     # ------------------------------------------------------------------ launch floor (N = 1)
     # What one launch costs beyond its work items, on the GPU alone: 100 launches of a small problem are
     # captured in a CUDA graph (the host cannot issue 10 us kernels fast enough through Python) and
@@ -540,6 +563,8 @@ def main():
             "gpu_launches": launches,
             "parity": par,
         }
+        if operator is not None:
+            line["operator"] = operator
         if sustained is not None:
             line["sustained"] = sustained
         if launch_floor is not None:
