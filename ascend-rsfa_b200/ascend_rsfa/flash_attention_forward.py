@@ -96,6 +96,10 @@ def _forward(q, k, v, causal, sm_scale, BM, BN, want_lse):
     if k.device != q.device or v.device != q.device:
         raise ValueError("q, k, v must live on one device")
     Z, H, N_CTX, HEAD_DIM = q.shape
+    if q.numel() == 0:
+        # an empty batch, head count or sequence: nothing to launch (the C ABI itself wants B, H, S >= 1)
+        return (torch.empty_like(q),
+                torch.empty((Z, H, N_CTX), dtype=torch.float32, device=q.device) if want_lse else None)
     qd, kd, vd = _dense(q.detach()), _dense(k.detach()), _dense(v.detach())
     o = torch.empty_like(qd)
     if not (o.stride(-1) == 1 and all(o.shape[i] == 1 or o.stride(i) % 8 == 0 for i in range(3))):
@@ -183,6 +187,8 @@ def attention_host(q, k, v, causal, sm_scale, BM=128, BN=128, device=0, out=None
     Z, H, N_CTX, HEAD_DIM = q.shape
     if out is None:
         out = torch.empty(q.shape, dtype=q.dtype, pin_memory=q.is_pinned())
+    if q.numel() == 0:
+        return out
     rc = _lib.rsfa_fwd_host(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), None,
                             Z, H, N_CTX, HEAD_DIM, 1 if causal else 0, float(sm_scale), int(BM), int(BN),
                             _DTYPES[q.dtype], int(device))

@@ -598,6 +598,19 @@ def test_device_argument_errors(fa, cuda_device):
     assert fa.get_num_compute_cores() >= 100
 
 
+def test_empty_batch_heads_or_sequence_launch_nothing(fa, cuda_device):
+    for shape in ((0, 4, 128, 64), (2, 0, 128, 64), (2, 4, 0, 128)):
+        q = torch.zeros(shape, dtype=torch.float16, device=cuda_device)
+        n0 = fa.launch_count()
+        o = fa.attention(q, q, q, True, 0.5, 128, 128)
+        o2, lse = fa.attention_with_lse(q, q, q, False, 0.5)
+        assert o.shape == q.shape and o2.shape == q.shape and o.dtype == q.dtype
+        assert lse.shape == q.shape[:3] and lse.dtype == torch.float32
+        assert fa.launch_count() == n0
+    h = torch.zeros(0, 2, 64, 64, dtype=torch.float16)
+    assert fa.attention_host(h, h, h, False, 0.5).shape == h.shape
+
+
 def test_launch_counter_counts_kernels(fa, cuda_device):
     q = torch.zeros(1, 1, 256, 128, dtype=torch.float16, device=cuda_device)
     n0 = fa.launch_count()
