@@ -23,13 +23,6 @@ struct FwdParams {
   int bf16;
   int tile_n;   // keys per tile on the tcgen05 path: 128 (single-buffered S) or 64 (double-buffered S)
   int variant;  // the "tcgen05_variant" option: -1 automatic, 0 / 1 / 2 force a kernel of the family
-  // Scratch of the D = 64 "separate P" kernel, which cannot redo a key tile itself: a counter, one
-  // flag per work item and the list of the items to run again.  Null when the caller has none (the
-  // kernel is then not used).
-  int* redo_count;
-  int* redo_flags;
-  int* redo_list;
-  int redo_capacity;   // work items the scratch has room for
   int* status;                 // device status word, never null
   // Work queue of the persistent kernels: word [0] hands out work items, word [1] counts the CTAs
   // that have finished.  Both are zero before a launch; the CTA that finishes last puts them back
@@ -70,11 +63,8 @@ cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t st
 // The double-buffered-S family (D = 64, 128, 256), selected by launch_fwd_tcgen05.
 cudaError_t launch_fwd_tcgen05_db(const FwdParams& p, int sm_count, cudaStream_t stream,
                                   long long* launches);
-// The D = 64 kernel with P in tensor-memory columns of its own (fwd_tcgen05_sp.cu).  It marks the work
-// items whose sum check failed in p.redo_*; launch_fwd_tcgen05 runs those again.
+// The D = 64 kernel with P in tensor-memory columns of its own (fwd_tcgen05_sp.cu), selected by launch_fwd_tcgen05.
 cudaError_t launch_fwd_tcgen05_sp(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches);
-// Number of work items (batch * head, block of 256 rows) of a problem in that kernel.
-int tcgen05_sp_items(const FwdParams& p);
 // Tile the tcgen05 family runs for a problem: the requested (block_m, block_n) when that tile is
 // instantiated for D, otherwise the tile table's row for (S, D, causal).  `variant` = -1 lets the
 // request / table decide, 0 forces 128-key tiles with single-buffered S, 1 forces 64-key tiles (D <= 128

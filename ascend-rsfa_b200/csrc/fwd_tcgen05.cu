@@ -116,13 +116,6 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint64_t wait_ns = p.wait_limit_ns;
-  // Redo mode with nothing to redo (the usual case): leave before anything is set up.  The count is
-  // written by the kernel in front of this one, so it is read only once that kernel has completed.
-  if (sched.redo_count != nullptr) {
-    griddep_wait();
-    if (*reinterpret_cast<const volatile int*>(sched.redo_count) == 0) return;
-  }
-
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int t = 0; t < kNT; ++t) {
@@ -194,15 +187,8 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
         if (!ok) break;
         // The first item of a CTA is its own index (the grid is never larger than the number of items): no
         // round trip to the queue stands before the first loads.  The queue hands out the items behind those.
-        int item;
-        if (sched.redo_count != nullptr) {
-          item = static_cast<int>(atomicAdd(p.tile_counter, 1u));
-          item = (item < *sched.redo_count) ? sched.redo_list[item] : sched.total_items;
-        } else if (item_count == 0) {
-          item = static_cast<int>(blockIdx.x);
-        } else {
-          item = static_cast<int>(atomicAdd(p.tile_counter, 1u) + gridDim.x);
-        }
+        const int item = (item_count == 0) ? static_cast<int>(blockIdx.x)
+                                           : static_cast<int>(atomicAdd(p.tile_counter, 1u) + gridDim.x);
         sched_ring[slot] = item;
         __threadfence_block();
         mbar_arrive(bar_sched_full0 + 8u * slot);
@@ -680,8 +666,7 @@ fwd_tcgen05_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, cons
 }
 
 template <int D, bool kBf16>
-cudaError_t launch_one(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches,
-                       bool redo_mode = false) {
+cudaError_t launch_one(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches) {
   using C = Cfg<D>;
   TmaMaps maps;
   if (!make_map(&maps.q, p.q, p, p.q_stride, kTileM) || !make_map(&maps.k, p.k, p, p.k_stride, kTileN) ||
@@ -690,8 +675,6 @@ cudaError_t launch_one(const FwdParams& p, int sm_count, cudaStream_t stream, lo
   SchedInfo sched;
   sched.items_per_head = (p.S + kNT * kTileM - 1) / (kNT * kTileM);
   sched.total_items = sched.items_per_head * p.B * p.H;
-  sched.redo_list = redo_mode ? p.redo_list : nullptr;
-  sched.redo_count = redo_mode ? p.redo_count : nullptr;
   auto kern = fwd_tcgen05_kernel<D, kBf16>;
   static std::atomic<unsigned long long> smem_done{0};   // per kernel instantiation, bit per device
   cudaError_t e = set_dynamic_smem_once(smem_done, reinterpret_cast<const void*>(kern), C::kSmemBytes);
@@ -752,19 +735,11 @@ cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t st
   if (p.D == 128) return p.bf16 ? launch_one<128, true>(p, sm_count, stream, launches)
                                 : launch_one<128, false>(p, sm_count, stream, launches);
   if (p.D <= 64) {
-    // D = 64 (and below): the separate-P kernel first (it marks the work items whose sum check failed and leaves
-    // their output undefined), then this file's kernel over the marked items only; that second
-    // launch returns at once when there are none.  Without scratch for the marks, or when single-
-    // buffered S is forced, this file's kernel does everything.
-    // A single key tile (S <= 128) leaves nothing to overlap: one launch of this file's kernel then.
-    const bool sp = p.variant != 0 && p.redo_count != nullptr && tcgen05_sp_items(p) <= p.redo_capacity &&
-                    (p.S > kTileN || p.variant == 2);
-    if (sp) {
-      const cudaError_t e = launch_fwd_tcgen05_sp(p, sm_count, stream, launches);
-      if (e != cudaSuccess) return e;
-    }
-    return p.bf16 ? launch_one<64, true>(p, sm_count, stream, launches, sp)
-                  : launch_one<64, false>(p, sm_count, stream, launches, sp);
+    // D = 64 (and below): the separate-P kernel, unless single-buffered S is forced.  A single key
+    // tile (S <= 128) leaves nothing to overlap: this file's kernel then.
+    if (p.variant != 0 && (p.S > kTileN || p.variant == 2)) return launch_fwd_tcgen05_sp(p, sm_count, stream, launches);
+    return p.bf16 ? launch_one<64, true>(p, sm_count, stream, launches)
+                  : launch_one<64, false>(p, sm_count, stream, launches);
   }
   return cudaErrorInvalidValue;
 }
@@ -903,10 +878,6 @@ extern "C" int rsfa_fwd_noalloc(const void* q, const void* k, const void* v, voi
   p.pdl = 0;                        // a memset precedes the kernel on the stream: nothing to overlap with
   p.test_drop_load = option_test_drop_load();
   p.variant = -1;
-  p.redo_count = nullptr;   // no scratch for the D = 64 separate-P kernel here: the 128-key kernel runs
-  p.redo_flags = nullptr;
-  p.redo_list = nullptr;
-  p.redo_capacity = 0;
 #ifdef RSFA_TRACE
   p.trace = nullptr;
 #endif

@@ -651,8 +651,6 @@ cudaError_t launch_db(const FwdParams& p, int sm_count, cudaStream_t stream, lon
   SchedInfo sched;
   sched.items_per_head = (p.S + NT * kRowsDb - 1) / (NT * kRowsDb);
   sched.total_items = sched.items_per_head * p.B * p.H;
-  sched.redo_list = nullptr;
-  sched.redo_count = nullptr;
   auto kern = fwd_tcgen05_db_kernel<D, NT, kBf16>;
   static std::atomic<unsigned long long> smem_done{0};   // per kernel instantiation, bit per device
   cudaError_t e = set_dynamic_smem_once(smem_done, reinterpret_cast<const void*>(kern), C::kSmemBytes);

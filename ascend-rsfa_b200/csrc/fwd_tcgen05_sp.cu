@@ -20,12 +20,18 @@
 //                            sum, sum check, wait until PV of tile j-1 has read P_t, tcgen05.st P_t
 //   O_t += P_t V_j           8 MMAs 128 x 64 x 16, A = P_t from TMEM, B = V_j MN-major
 // The softmax keeps no per-tile row maximum (see softmax_half_careful in tcgen05_common.cuh for
-// the scheme).  Because S_t is gone by the time the sum check can fail, this kernel cannot redo a
-// tile: a failed check marks the work item in `redo_flags`, the item's output is left undefined,
-// and the launcher runs the marked items again with the 128-key kernel of fwd_tcgen05.cu, which
-// can.  When many items fail (more than one in kBailOneIn of those started), the producer warps
-// move the rest of the queue to the redo list uncomputed.
+// the scheme): P is taken against a reference fixed at the first key tile, and a check of each
+// tile's row sums says whether a P value may have left the 16-bit range.  Because S_t is gone by
+// the time that check can fail, the fast loop cannot repair a tile.  A work item with a failed
+// check is therefore run a second time by the same CTA, as its next item, with the "safe" loop:
+// that one checks each 64-key half while its scores are still in registers and, when a half is
+// over the limit, moves the rows' reference up by a whole number of binary orders and brings l,
+// the tile's first half and O_t along (about a sixth slower per step, so it is not the default).
+// A CTA that has had to repeat more than one item in kBailOneIn stops trying the fast loop.
+// Everything is local to the CTA: no list in global memory, no second launch.
 #include <cuda.h>
+
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -43,8 +49,9 @@ constexpr int kThreadsSp = 384;
 constexpr int kTmaWarpSp = 8;
 constexpr int kMmaWarpSp0 = 9;  // warps 9, 10: one issuer per Q tile
 constexpr int kStagesSp = 6;
-constexpr int kBailOneIn = 8;        // give up on this kernel when more than 1 item in 8 has to be redone
-constexpr int kBailRounds = 2;       // ... but not before every CTA has started this many items
+constexpr int kBailOneIn = 4;        // a CTA gives up on the fast loop when more than 1 item in 4 had to be repeated,
+constexpr int kBailMin = 2;          // ... and at least this many were
+constexpr int kSafeItem = 1 << 30;   // flag on a work item number in the scheduler ring: run it with the safe loop
 constexpr int kQBytes = kRows * kD * 2;      // 16 KB
 constexpr int kKvBytes = kKeys * kD * 2;     // 16 KB
 constexpr int kStageBytesSp = kRows * 128;   // epilogue staging per Q tile: 128 rows x 64 columns
@@ -83,11 +90,13 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   const uint32_t bar_sched_full0 = sBar + 8u * (7 * kTiles + 2 * kStagesSp);   // 2 slots
   const uint32_t bar_sched_empty0 = bar_sched_full0 + 16u;                     // 2 slots
   const uint32_t misc = sBar + 8u * kNumBarriersSp;
-  // misc words: [0] TMEM base, [1] abort flag, [2..3] scheduler ring
+  // misc words: [0] TMEM base, [1] abort flag, [2..3] scheduler ring, [4..5] "the item of this ring slot
+  // failed a sum check" (set by its softmax warps before they give the slot back)
   uint8_t* misc_ptr = smem_raw + (misc - smem_u32(smem_raw));
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(misc_ptr);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc_ptr + 4);
   volatile int* sched_ring = reinterpret_cast<volatile int*>(misc_ptr + 8);
+  volatile int* item_failed = reinterpret_cast<volatile int*>(misc_ptr + 16);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -95,6 +104,8 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    item_failed[0] = 0;
+    item_failed[1] = 0;
     for (int t = 0; t < kTiles; ++t) {
       mbar_init(bar_q_full(t), 1);
       mbar_init(bar_q_empty(t), 1);
@@ -110,7 +121,9 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_sched_full0 + 8u * s, 1);
-      mbar_init(bar_sched_empty0 + 8u * s, kTiles + kTiles * 4);  // MMA lanes + one lane per softmax warp
+      // the MMA warps give a slot back when they have read it, the softmax warps (one lane each) only
+      // when they are done with the item: a free slot means that its item's sum checks are known
+      mbar_init(bar_sched_empty0 + 8u * s, kTiles + kTiles * 4);
     }
     fence_barrier_init();
     fence_proxy_async();
@@ -150,36 +163,54 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       // ================================================================ producer
       if (lane == 0) {
         uint32_t kv_count = 0, item_count = 0;
+        int dispatched[2] = {0, 0};        // item of each ring slot
+        int n_fast = 0, n_failed = 0;      // items tried with the fast loop / of those, repeated
+        bool queue_empty = false;
         bool ok = true;
         while (ok) {
           const int slot = item_count & 1;
-          // (read before the wait below, which hides the latency of the load)
-          int failed = *static_cast<volatile int*>(p.redo_count);
           ok = mbar_wait(bar_sched_empty0 + 8u * slot, ((item_count >> 1) & 1) ^ 1, abort_flag, wait_ns, kTagSched);
           if (!ok) break;
-          // Next work item.  When more than one item in kBailOneIn has failed its sum check so far
-          // (rows close to one-hot: the data do not suit this kernel), the rest of the queue is not
-          // computed here at all but put on the redo list at once, so that the launch costs little
-          // more than the 128-key kernel alone would have.  The first kBailRounds items of every CTA always run.
-          int item;
-          for (;;) {
-            // the first item of a CTA is its own index (grid <= number of items), the queue hands out the rest
+          // The item that had this slot (two items ago) is finished.  If one of its sum checks failed,
+          // it is the next item, with the safe loop; else the queue's next one (the first item of a CTA
+          // is its own index: grid <= number of items), fast unless this CTA has given up on that.
+          int item = sched.total_items;
+          auto take_failed = [&](int sl) {
+            if (item_failed[sl] != 0) {
+              item_failed[sl] = 0;
+              ++n_failed;
+              item = dispatched[sl] | kSafeItem;
+            }
+          };
+          if (item_count >= 2) take_failed(slot);
+          if (item == sched.total_items && !queue_empty) {
             item = (item_count == 0) ? static_cast<int>(blockIdx.x)
                                      : static_cast<int>(atomicAdd(p.tile_counter, 1u) + gridDim.x);
-            if (item >= sched.total_items || item < kBailRounds * static_cast<int>(gridDim.x)) break;
-            if (failed * kBailOneIn <= item) break;
-            if (atomicExch(&p.redo_flags[item], 1) == 0) p.redo_list[atomicAdd(p.redo_count, 1)] = item;
-            failed = *static_cast<volatile int*>(p.redo_count);
+            if (item >= sched.total_items) {
+              item = sched.total_items;
+              queue_empty = true;
+              griddep_launch_dependents();   // the queue is empty: the kernel behind this one may set up
+            } else if (n_failed >= kBailMin && n_failed * kBailOneIn > n_fast) {
+              item |= kSafeItem;
+            } else {
+              ++n_fast;
+            }
           }
+          if (item == sched.total_items && item_count >= 1) {
+            // Nothing left to hand out, but the item in the other slot is still running and may fail:
+            // wait for it (the wait the next dispatch would have done) before the CTA is told to leave.
+            ok = mbar_wait(bar_sched_empty0 + 8u * (slot ^ 1), (((item_count + 1) >> 1) & 1) ^ 1, abort_flag, wait_ns,
+                           kTagSched);
+            if (!ok) break;
+            take_failed(slot ^ 1);
+          }
+          dispatched[slot] = item & ~kSafeItem;
           sched_ring[slot] = item;
           __threadfence_block();
           mbar_arrive(bar_sched_full0 + 8u * slot);
-          if (item >= sched.total_items) {
-            griddep_launch_dependents();   // the queue is empty: the redo pass behind this kernel may set up
-            break;
-          }
+          if (item == sched.total_items) break;
           int bh, row0;
-          decode(item, bh, row0);
+          decode(item & ~kSafeItem, bh, row0);
           const int b = bh / p.H, h = bh - b * p.H;
           int nmax = 0;
           for (int t = 0; t < kTiles; ++t) nmax = max(nmax, num_kv_tiles_sp(row0 + t * kRows, S, p.causal));
@@ -232,7 +263,7 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         const int slot = item_count & 1;
         ok = wait_all(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, kTagSched);
         if (!ok) break;
-        const int item = __shfl_sync(0xffffffffu, sched_ring[slot], 0);
+        const int item = __shfl_sync(0xffffffffu, sched_ring[slot], 0) & ~kSafeItem;   // fast or safe: the same MMAs
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_sched_empty0 + 8u * slot);
         if (item >= sched.total_items) break;
@@ -333,25 +364,24 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
     const float headroom = kHeadroomLog2 / scale_log2;   // in raw score units (sm_scale > 0 on this path)
     uint32_t item_count = 0, s_count = 0, o_count = 0, pf_count = 0;
     bool ok = true;
-    while (ok) {
-      const int slot = item_count & 1;
-      ok = mbar_wait_warp(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
-      if (!ok) break;
-      const int item = sched_ring[slot];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_sched_empty0 + 8u * slot);
-      if (item >= sched.total_items) break;
-      ++item_count;
+
+    // One work item of this Q tile: key tiles, then the epilogue.  kSafe = false is the fast loop (one
+    // sum check per key tile; returns true if one failed: the item's output is then undefined and the
+    // item has to be run again), kSafe = true the loop that repairs a failed check in place.
+    auto run_item = [&](auto safe_tag, int item) __attribute__((always_inline)) -> bool {
+      constexpr bool kSafe = decltype(safe_tag)::value;
       int bh, row0;
       decode(item, bh, row0);
       const int tile_row0 = row0 + t * kRows;
       const int row = tile_row0 + row_in_tile;
       const int n_tiles = num_kv_tiles_sp(tile_row0, S, p.causal);
-      if (n_tiles == 0) continue;
+      if (n_tiles == 0) return false;
 
-      float m_used = -INFINITY;  // reference, in raw score units: first key tile's maximum + headroom
+      // Row state: x = s * scale_log2 + neg_m is the exponent of a score against the row's reference
+      // (first key tile's maximum + headroom; the safe loop moves it up when a check fails), l = sum of P.
+      float neg_m = 0.f;
       float l = 0.f;
-      bool overflow = false;     // a sum check failed: this item has to be run again
+      bool overflow = false;
       for (int j = 0; j < n_tiles; ++j) {
         ok = mbar_wait_warp(bar_s_full(t), s_count & 1, abort_flag, wait_ns, kTagSFull);
         if (!ok) break;
@@ -405,11 +435,10 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           }
           float mb = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
           if (mb == -INFINITY) mb = 0.f;  // only rows past S can get here; keep them finite
-          m_used = mb + headroom;
+          neg_m = -(mb + headroom) * scale_log2;
         }
         const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
-        const float neg_m = -m_used * scale_log2;
-        const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
+        uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
         uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
         // exp2, row sum and 16-bit packing of 32 scores into pk[base .. base+16)
         auto exp_pack = [&](uint32_t (&sv)[32], uint32_t (&pk)[32], int base) {
@@ -427,17 +456,94 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
             pk[base + (c >> 1) + 1] = pack2<kBf16>(e2, e3);
           }
         };
+        auto take_sum = [&]() -> float {
+          float a0, a1;
+          unpack_f32x2(add_f32x2(sum_a, sum_b), a0, a1);
+          sum_a = pack_f32x2(0.f, 0.f);
+          sum_b = sum_a;
+          return a0 + a1;
+        };
         uint32_t pk0[32], pk1[32];
-        exp_pack(s0, pk0, 0);
-        exp_pack(s1, pk0, 16);
-        exp_pack(s2, pk1, 0);
-        exp_pack(s3, pk1, 16);
-        float a0, a1;
-        unpack_f32x2(add_f32x2(sum_a, sum_b), a0, a1);
-        const float h = a0 + a1;
-        // Every P value is bounded by the sum; !(h <= limit) also catches NaN and +inf.
-        overflow = overflow || !(h <= kSumLimit);
-        l += h;
+        if constexpr (!kSafe) {
+          exp_pack(s0, pk0, 0);
+          exp_pack(s1, pk0, 16);
+          exp_pack(s2, pk1, 0);
+          exp_pack(s3, pk1, 16);
+          const float h = take_sum();
+          // Every P value is bounded by the sum; !(h <= limit) also catches NaN and +inf.
+          if (__any_sync(0xffffffffu, !(h <= kSumLimit))) overflow = true;
+          l += h;
+        } else {
+          // A half (64 keys) whose sum is over the limit may hold values beyond the 16-bit range.  Its
+          // scores are still in registers: the rows concerned move their reference up by a whole
+          // number of binary orders, so that the half's maximum sits `headroom` below it again; l,
+          // this tile's first half (already packed: the factor is a power of two, so this is exact
+          // short of underflow) and O_t follow, and the half is computed again.  Rows that were fine
+          // go through it with a factor of one.  All 32 lanes run it together.
+          auto repair = [&](uint32_t (&sx)[32], uint32_t (&sy)[32], uint32_t (&pk)[32], bool second, float& h_this,
+                            float& h_first) -> bool {
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 32; c += 4) {
+              mx[0] = max3(mx[0], __uint_as_float(sx[c]), __uint_as_float(sx[c + 1]));
+              mx[1] = max3(mx[1], __uint_as_float(sx[c + 2]), __uint_as_float(sx[c + 3]));
+              mx[2] = max3(mx[2], __uint_as_float(sy[c]), __uint_as_float(sy[c + 1]));
+              mx[3] = max3(mx[3], __uint_as_float(sy[c + 2]), __uint_as_float(sy[c + 3]));
+            }
+            const float mb = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            float shift = 0.f;
+            if (!(h_this <= kSumLimit)) shift = ceilf(fmaf(mb, scale_log2, neg_m) + kHeadroomLog2);
+            if (!(shift >= 0.f)) shift = 0.f;   // NaN scores: nothing sensible to do, and nothing to get stuck in
+            const float alpha = shift <= 126.f ? __int_as_float((127 - static_cast<int>(shift)) << 23) : 0.f;
+            neg_m -= shift;
+            neg_m2 = pack_f32x2(neg_m, neg_m);
+            l *= alpha;
+            if (second) {
+              h_first *= alpha;
+#pragma unroll
+              for (int c = 0; c < 32; ++c) {
+                float f0, f1;
+                unpack2<kBf16>(pk0[c], f0, f1);
+                pk0[c] = pack2<kBf16>(f0 * alpha, f1 * alpha);
+              }
+            }
+            if (j > 0) {
+              // O_t holds the key tiles before this one, complete once the PV MMAs of tile j-1 are
+              if (!mbar_wait_warp(bar_p_free(t), (pf_count + j - 1) & 1, abort_flag, wait_ns, kTagPvDone)) return false;
+              tc_fence_after_sync();
+#pragma unroll 1
+              for (int c0 = 0; c0 < kD; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld_x32(tO + c0, o);
+                tmem_wait_ld();
+                reg_fence_x32(o);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+                tmem_st_x32(tO + c0, o);
+              }
+            }
+            exp_pack(sx, pk, 0);
+            exp_pack(sy, pk, 16);
+            h_this = take_sum();
+            return true;
+          };
+          exp_pack(s0, pk0, 0);
+          exp_pack(s1, pk0, 16);
+          float h0 = take_sum();
+          if (__any_sync(0xffffffffu, !(h0 <= kSumLimit))) {
+            float none = 0.f;
+            ok = repair(s0, s1, pk0, false, h0, none);
+            if (!ok) break;
+          }
+          exp_pack(s2, pk1, 0);
+          exp_pack(s3, pk1, 16);
+          float h1 = take_sum();
+          if (__any_sync(0xffffffffu, !(h1 <= kSumLimit))) {
+            ok = repair(s2, s3, pk1, true, h1, h0);
+            if (!ok) break;
+          }
+          l += h0 + h1;
+        }
         // P_t still belongs to the PV MMAs of the previous key tile until they have completed.
         if (j > 0) {
           ok = mbar_wait_warp(bar_p_free(t), (pf_count + j - 1) & 1, abort_flag, wait_ns, kTagPvDone);
@@ -450,18 +556,18 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         tc_fence_before_sync();
         mbar_arrive(bar_p_full(t));
       }
-      if (!ok) break;
+      if (!ok) return false;
       pf_count += n_tiles;
-      if (__any_sync(0xffffffffu, overflow) && lane == 0 && atomicExch(&p.redo_flags[item], 1) == 0)
-        p.redo_list[atomicAdd(p.redo_count, 1)] = item;   // first warp to mark the item also lists it
 
-      // ---- epilogue: O_t / l -> global, lse = m + log l
+      // ---- epilogue: O_t / l -> global, lse = reference + log l
       ok = mbar_wait_warp(bar_o_full(t), o_count & 1, abort_flag, wait_ns, kTagOFull);
-      if (!ok) break;
+      if (!ok) return false;
       ++o_count;
       tc_fence_after_sync();
       const float inv_l = 1.f / l;
       const int b = bh / p.H, h = bh - b * p.H;
+      // A repeated item writes the rows its first attempt wrote: those stores must have landed first.
+      if (kSafe && lane == 0) tma_store_wait_all();
       // O_t / l -> global memory: each warp stages and stores its own 32 rows (store_o_rows)
       {
         const int wq = warp & 3;
@@ -469,8 +575,27 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
                                 tile_row0 + wq * 32, h, b, tile_row0 + wq * 32 < S);
       }
       if (p.lse != nullptr && row < S)
-        p.lse[static_cast<int64_t>(bh) * S + row] = m_used * p.sm_scale + logf(l);
+        p.lse[static_cast<int64_t>(bh) * S + row] = -neg_m * kLn2 + logf(l);
       tc_fence_before_sync();
+      return overflow;
+    };
+
+    while (ok) {
+      const int slot = item_count & 1;
+      ok = mbar_wait_warp(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, abort_flag, wait_ns, kTagSched);
+      if (!ok) break;
+      const int item = sched_ring[slot];
+      if (item == sched.total_items) break;
+      ++item_count;
+      const bool failed = (item & kSafeItem) != 0 ? run_item(std::true_type{}, item & ~kSafeItem)
+                                                  : run_item(std::false_type{}, item);
+      if (!ok) break;
+      // Done with the item: the ring slot goes back, with the news if it has to be run again.
+      __syncwarp();
+      if (lane == 0) {
+        if (failed) item_failed[slot] = 1;
+        mbar_arrive(bar_sched_empty0 + 8u * slot);
+      }
     }
     if (lane == 0) tma_store_wait_all();   // the last TMA stores must be complete before the CTA exits
   }
@@ -494,8 +619,6 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
 
 }  // namespace
 
-// Launches the kernel over all work items of `p` after clearing p.redo_count and p.redo_flags on the
-// same stream; afterwards p.redo_list[0 .. *p.redo_count) names the items whose sum check failed.
 template <bool kBf16>
 static cudaError_t launch_sp_one(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches) {
   TmaMaps maps;
@@ -505,20 +628,13 @@ static cudaError_t launch_sp_one(const FwdParams& p, int sm_count, cudaStream_t 
   SchedInfo sched;
   sched.items_per_head = (p.S + kTiles * kRows - 1) / (kTiles * kRows);
   sched.total_items = sched.items_per_head * p.B * p.H;
-  sched.redo_list = nullptr;
-  sched.redo_count = nullptr;
-  if (p.redo_count == nullptr || p.redo_flags != p.redo_count + 4 || sched.total_items > p.redo_capacity)
-    return cudaErrorInvalidValue;
   auto kern = fwd_tcgen05_sp_kernel<kBf16>;
   static std::atomic<unsigned long long> smem_done{0};   // per kernel instantiation, bit per device
   cudaError_t e = set_dynamic_smem_once(smem_done, reinterpret_cast<const void*>(kern), kSmemBytesSp);
   if (e != cudaSuccess) return e;
-  // The redo counter (padded to 4 words) and the flags are one block, cleared for every call.  The work
-  // queue needs no memset: the last CTA of the launch that used it before put it back to zero.
-  e = cudaMemsetAsync(p.redo_count, 0, (4 + static_cast<size_t>(sched.total_items)) * sizeof(int), stream);
-  if (e != cudaSuccess) return e;
+  // No memset of the work queue: the last CTA of the launch that used it before put it back to zero.
   const int grid = sched.total_items < sm_count ? sched.total_items : sm_count;
-  e = launch_persistent(kern, grid, kThreadsSp, kSmemBytesSp, stream, false, maps, p, sched);
+  e = launch_persistent(kern, grid, kThreadsSp, kSmemBytesSp, stream, p.pdl != 0, maps, p, sched);
   if (e == cudaSuccess) *launches += 1;
   return e;
 }
@@ -527,10 +643,6 @@ cudaError_t launch_fwd_tcgen05_sp(const FwdParams& p, int sm_count, cudaStream_t
   if (p.D > kD) return cudaErrorInvalidValue;   // D < 64: zero columns from the tensor maps
   return p.bf16 ? launch_sp_one<true>(p, sm_count, stream, launches)
                 : launch_sp_one<false>(p, sm_count, stream, launches);
-}
-
-int tcgen05_sp_items(const FwdParams& p) {
-  return ((p.S + kTiles * kRows - 1) / (kTiles * kRows)) * p.B * p.H;
 }
 
 }  // namespace rsfa

@@ -16,13 +16,6 @@ namespace {
 
 constexpr int kMaxDevices = 64;
 constexpr int kCounterSlots = 1024;  // one work queue (two words) per launch in flight
-// Scratch of the D = 64 separate-P kernel: kRedoSlots blocks, each
-// [counter padded to 4 ints][kRedoCapacity flags][kRedoCapacity item ids].  A call takes a block whose
-// last user has finished on the GPU (an event per block says so); larger problems, and calls that
-// find every block still in use, run the 128-key kernel alone.
-constexpr int kRedoSlots = 8;
-constexpr int kRedoCapacity = 1 << 18;
-constexpr size_t kRedoBlockInts = 4 + 2 * static_cast<size_t>(kRedoCapacity);
 
 struct DeviceState {
   bool ready = false;
@@ -32,11 +25,6 @@ struct DeviceState {
   int* status = nullptr;
   int* status_mirror = nullptr;      // pinned host copy of the status word (the "check_status" option)
   unsigned next_slot = 0;
-  int* redo = nullptr;               // kRedoSlots blocks, allocated at the first D = 64 call that can use them
-  cudaEvent_t redo_done[kRedoSlots] = {};   // recorded behind the last launches that used the block
-  bool redo_held[kRedoSlots] = {};          // a host thread is between taking the block and recording its event
-  bool redo_used[kRedoSlots] = {};          // the block has been used at all
-  cudaStream_t redo_stream[kRedoSlots] = {};   // stream of the block's last user
   // staging buffers of rsfa_fwd_host (grow-only)
   void* stage[2][4] = {{nullptr, nullptr, nullptr, nullptr}, {nullptr, nullptr, nullptr, nullptr}};
   float* stage_lse[2] = {nullptr, nullptr};
@@ -373,14 +361,9 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   p.trace = reinterpret_cast<unsigned long long*>(g_trace_ptr.load());
 #endif
   p.variant = static_cast<int>(g_tcgen05_variant.load());
-  p.redo_count = nullptr;
-  p.redo_flags = nullptr;
-  p.redo_list = nullptr;
-  p.redo_capacity = 0;
 
   long long launches = 0;
   cudaError_t e;
-  int redo_slot = -1;
   const int path = choose_path(S, D, sm_scale);
   // one CTA per (head, block of 64 rows), all on grid.x, whose limit is 2^31 - 1
   if (path == RSFA_PATH_GENERIC && rsfa::generic_grid_blocks(B, H, S) > 2147483647LL) return RSFA_ERR_TOO_LARGE;
@@ -389,68 +372,11 @@ int rsfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
     tile_of_path(path, S, D, causal, block_m, block_n, &bm, &bn);
     p.tile_n = bn;
   }
-  if (path == RSFA_PATH_TCGEN05 && D <= 64 && p.tile_n == 128 && p.variant != 0 &&
-      rsfa::tcgen05_sp_items(p) <= kRedoCapacity) {
-    std::lock_guard<std::mutex> lock(g_mu);
-    if (d->redo == nullptr) {
-      int prev = 0;
-      cudaGetDevice(&prev);
-      cudaSetDevice(device);
-      if (cudaMalloc(&d->redo, kRedoSlots * kRedoBlockInts * sizeof(int)) != cudaSuccess) {
-        cudaGetLastError();
-        d->redo = nullptr;   // no scratch: the 128-key kernel does the work
-      }
-      cudaSetDevice(prev);
-    }
-    // A block whose last user ran on this call's stream can be taken at once: stream order puts this
-    // call's memset and kernels behind that user's.  Otherwise a block that no host thread holds and
-    // whose last user has finished on the GPU (its event says so).  None free (eight such calls of other
-    // streams still in flight on this device): this call runs the 128-key kernel alone, which needs
-    // no scratch.
-    for (int i = 0; d->redo != nullptr && i < kRedoSlots && redo_slot < 0; ++i)
-      if (!d->redo_held[i] && d->redo_used[i] && d->redo_stream[i] == static_cast<cudaStream_t>(stream)) redo_slot = i;
-    for (int i = 0; d->redo != nullptr && i < kRedoSlots && redo_slot < 0; ++i) {
-      if (d->redo_held[i]) continue;
-      if (d->redo_done[i] == nullptr &&
-          cudaEventCreateWithFlags(&d->redo_done[i], cudaEventDisableTiming) != cudaSuccess) {
-        cudaGetLastError();
-        d->redo_done[i] = nullptr;
-        continue;
-      }
-      if (cudaEventQuery(d->redo_done[i]) == cudaSuccess) redo_slot = i;
-      else cudaGetLastError();
-    }
-    if (redo_slot >= 0) {
-      int* block = d->redo + redo_slot * kRedoBlockInts;
-      p.redo_count = block;
-      p.redo_flags = block + 4;
-      p.redo_list = block + 4 + kRedoCapacity;
-      p.redo_capacity = kRedoCapacity;
-      d->redo_held[redo_slot] = true;   // until the event is recorded behind this call's launches
-    }
-  }
   if (path == RSFA_PATH_TCGEN05)
     e = rsfa::launch_fwd_tcgen05(p, d->sm_count, static_cast<cudaStream_t>(stream), &launches);
   else
     e = rsfa::launch_fwd_generic(p, static_cast<cudaStream_t>(stream), &launches);
   g_launches.fetch_add(launches);
-  if (redo_slot >= 0) {
-    std::lock_guard<std::mutex> lock(g_mu);
-    if (d->redo_done[redo_slot] == nullptr &&
-        cudaEventCreateWithFlags(&d->redo_done[redo_slot], cudaEventDisableTiming) != cudaSuccess) {
-      cudaGetLastError();
-      d->redo_done[redo_slot] = nullptr;
-    }
-    // Without an event the block stays held for good: better one block less than one shared by two streams.
-    if (d->redo_done[redo_slot] != nullptr &&
-        cudaEventRecord(d->redo_done[redo_slot], static_cast<cudaStream_t>(stream)) == cudaSuccess) {
-      d->redo_used[redo_slot] = true;
-      d->redo_stream[redo_slot] = static_cast<cudaStream_t>(stream);
-      d->redo_held[redo_slot] = false;
-    } else {
-      cudaGetLastError();
-    }
-  }
   if (e == cudaSuccess && check_status) {
     // The status word follows the kernels to the host on the same stream; the next call looks at it.
     if (cudaMemcpyAsync(d->status_mirror, d->status, sizeof(int), cudaMemcpyDeviceToHost,

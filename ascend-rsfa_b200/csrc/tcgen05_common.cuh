@@ -12,6 +12,7 @@ namespace rsfa {
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
 #ifndef RSFA_SUM_LIMIT
 #define RSFA_SUM_LIMIT 32768.0f
 #endif
@@ -63,10 +64,6 @@ struct TmaMaps {
 struct SchedInfo {
   int total_items;
   int items_per_head;  // 256-row blocks per head
-  // Redo mode (both null otherwise): the queue hands out redo_list[0 .. *redo_count) instead of
-  // every item; a launch that finds *redo_count == 0 returns at once.
-  const int* redo_list;
-  const int* redo_count;
 };
 
 template <bool kBf16>
@@ -77,6 +74,18 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   } else {
     __half2 t = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&t);
+  }
+}
+
+template <bool kBf16>
+__device__ __forceinline__ void unpack2(uint32_t v, float& lo, float& hi) {
+  if constexpr (kBf16) {
+    lo = __uint_as_float(v << 16);
+    hi = __uint_as_float(v & 0xffff0000u);
+  } else {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
+    lo = f.x;
+    hi = f.y;
   }
 }
 

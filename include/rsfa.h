@@ -62,13 +62,10 @@ extern "C" {
  *   stream       a cudaStream_t (NULL = default stream).  The call is asynchronous like the
  *                reference's kernel launches; it does not synchronise.
  *
- * Concurrency: calls on different streams of one device may overlap on the GPU.  Every launch takes a
- * work queue of its own out of 1024 per device (the kernel puts it back to zero when it ends).  At
- * D <= 64 with 128-key tiles a call is two launches that share a scratch block, one of eight per
- * device: a call reuses the block it used last on the same stream, takes another one only when the
- * event recorded behind that block's last user has completed, and runs the single-launch 128-key
- * kernel when none is free (more than eight such calls of different streams in flight).  The status
- * word is shared per device.
+ * Concurrency: calls on different streams of one device may overlap on the GPU.  Every call is one
+ * kernel launch and takes a work queue of its own out of 1024 per device (the kernel puts it back to
+ * zero when it ends); nothing else in device memory is shared between calls except the status word,
+ * which is per device.
  *
  * Errors: D outside {16,32,64,128,256} or mismatched (the reference asserts, :551-554), B/H/S < 1,
  * misaligned pointers or strides -> RSFA_ERR_INVALID_ARGUMENT.  A device status left by an earlier
@@ -102,8 +99,8 @@ RSFA_API int rsfa_fwd_host(const void* q_host, const void* k_host, const void* v
  * process exits) and calls no cudaMalloc, cudaFree or other allocating routine.
  *
  * Arguments as rsfa_fwd, without block_m / block_n: the tile table decides, so either tcgen05
- * kernel family may run (64-key tiles at D = 256 and for short causal sequences, 128-key
- * tiles otherwise; the D = 64 separate-P kernel, whose redo list is allocated scratch, is not used).
+ * kernel family may run, as in rsfa_fwd (64-key tiles at D = 256 and for short causal sequences,
+ * 128-key tiles otherwise, the separate-P kernel at D <= 64).
  * Every in-kernel wait is bounded by the "wait_limit_ms" option, as in rsfa_fwd.  Limits: only
  * shapes the tcgen05 kernels are built for (sm_scale > 0; D = 16 and 32 run on the D = 64 kernel) -> otherwise
  * RSFA_ERR_UNSUPPORTED; at most 2^30 work items (B * H * ceil(S / 256), or ceil(S / 128) at D = 256), because the queue counter

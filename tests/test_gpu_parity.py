@@ -169,26 +169,45 @@ def test_short_sequences_on_both_kernel_families(fa, cuda_device, causal):
         assert fa.work_items(B, H, S, D, causal, scale) == B * H * (1 if on_tcgen05 else -(-S // 64))
 
 
-def test_separate_p_kernel_marks_items_and_they_are_run_again(fa, cuda_device):
-    # D = 64 with 128-key tiles runs two launches: the separate-P kernel, which cannot redo a key
-    # tile and marks the work items whose sum check failed, and the 128-key kernel over the marked
-    # items.  Near one-hot rows with a growing maximum (sm_scale 3) mark many items; flat rows none.
-    # Both must match the oracle, and the launch counter must show the two launches.
+def test_separate_p_kernel_repeats_items_whose_sum_check_failed(fa, cuda_device):
+    # D = 64 with 128-key tiles: the fast loop of the separate-P kernel cannot repair a key tile; a work
+    # item whose sum check failed is run again by the same CTA with the loop that can.  Near one-hot rows
+    # with a growing maximum (sm_scale 3) fail in many items; flat rows in none.  Both must match the
+    # oracle, and each call is one launch.
     q, k, v = make_inputs(2, 3, 1024, 64, seed=31)
     n0 = fa.launch_count()
     check(fa, q, k, v, False, 3.0, 128, 128, cuda_device)
     check(fa, q, k, v, True, 3.0, 128, 128, cuda_device)
     check(fa, q, k, v, False, 0.125, 128, 128, cuda_device)
-    assert fa.launch_count() - n0 == 6
+    assert fa.launch_count() - n0 == 3
 
 
-def test_separate_p_kernel_gives_up_on_a_batch_of_one_hot_rows(fa, cuda_device):
-    # 512 work items, more than two per CTA: once more than one item in eight has failed its sum
-    # check, the separate-P kernel puts the rest of its queue on the redo list without computing
-    # it.  Every item must still come out right, whichever of the two kernels produced it.
+def test_separate_p_kernel_gives_up_on_the_fast_loop_for_one_hot_rows(fa, cuda_device):
+    # 512 work items, more than three per CTA: a CTA that has had to repeat more than one item in four
+    # runs the rest of its items with the repairing loop at once.  Every item must still come out
+    # right, whichever loop produced it; bf16 and a ragged length go through the same paths.
     q, k, v = make_inputs(4, 64, 512, 64, seed=37)
     check(fa, q, k, v, False, 3.0, 128, 128, cuda_device)
     check(fa, q, k, v, True, 3.0, 128, 128, cuda_device)
+    q, k, v = make_inputs(2, 40, 1000, 64, seed=38, dtype=torch.bfloat16)
+    check(fa, q, k, v, False, 3.0, 128, 128, cuda_device)
+    check(fa, q, k, v, True, 3.0, 128, 128, cuda_device)
+
+
+def test_repairing_loop_follows_a_maximum_that_keeps_growing(fa, cuda_device):
+    # Keys sorted so that every row's largest scores come last, with a wide spread: the first attempt
+    # fails early, and the repeat has to move its reference up again and again, in the first and in the
+    # second half of a key tile, rescaling O each time.  D = 32 runs on the same kernel.
+    for D in (64, 32):
+        g = torch.Generator().manual_seed(5 + D)
+        S = 2048
+        k = torch.randn(1, 2, S, D, generator=g)
+        ramp = torch.linspace(0.05, 3.0, S).view(1, 1, S, 1)
+        k = (k.sign() * ramp).to(torch.float16)          # |k| grows with the key index
+        q = (torch.randn(1, 2, S, D, generator=g).sign()).to(torch.float16)
+        v = torch.randn(1, 2, S, D, generator=g).to(torch.float16)
+        for causal in (False, True):
+            check(fa, q, k, v, causal, 1.0, 128, 128, cuda_device)
 
 
 def test_result_does_not_depend_on_requested_tile(fa, cuda_device):
@@ -307,13 +326,13 @@ def test_cfg4_shape_long_sequence_d128(fa, cuda_device, causal):
 @pytest.mark.parametrize("variant", [-1, 0, 1, 2])
 @pytest.mark.parametrize("causal", [False, True])
 def test_cfg5_shape_very_long_small_head_wide_logits(fa, cuda_device, causal, variant):
-    # 64 key tiles of 128 per row; variant -1 / 2 = separate-P kernel + redo pass, 0 = 128-key kernel
-    # alone, 1 = 64-key kernel.  Inputs x 2.0 widen the logits (std 5.8 log2 units).
+    # 64 key tiles of 128 per row; variant -1 / 2 = separate-P kernel, 0 = 128-key kernel, 1 = 64-key
+    # kernel: one launch each.  Inputs x 2.0 widen the logits (std 5.8 log2 units).
     fa.set_option("tcgen05_variant", variant)
     try:
         n0 = fa.launch_count()
         _check_config_shape(fa, cuda_device, "cfg5", 1, 4, causal, 128, 128)
-        assert fa.launch_count() - n0 == (2 if variant in (-1, 2) else 1)
+        assert fa.launch_count() - n0 == 1
     finally:
         fa.set_option("tcgen05_variant", -1)
 
@@ -402,11 +421,10 @@ def test_check_status_option_makes_the_next_call_fail(fa, cuda_device):
     fa.device_status()
 
 
-def test_d64_calls_on_several_streams_do_not_share_redo_scratch(fa, cuda_device):
-    # At D = 64 a call is two launches that share a scratch block (marks of the work items to run
-    # again).  Calls that are in flight at the same time on different streams must each get a block
-    # of their own, or run the kernel that needs none: near one-hot rows (sm_scale 3) mark many items,
-    # so a block shared by two calls would lose marks and leave wrong output.
+def test_d64_calls_on_several_streams_keep_their_repeats_apart(fa, cuda_device):
+    # Calls in flight at the same time on different streams, on data whose sum checks fail in many
+    # work items (near one-hot rows, sm_scale 3): which items are repeated is known only inside each
+    # CTA, so nothing is shared between the calls and every one must come out right.
     q, k, v = make_inputs(2, 3, 1024, 64, seed=31)
     ref = {c: attention_fp32(q, k, v, c, 3.0) for c in (False, True)}
     qd, kd, vd = [t.to(cuda_device) for t in (q, k, v)]

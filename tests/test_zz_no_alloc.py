@@ -48,15 +48,9 @@ def test_noalloc_matches_regular_entry_point_twice(cuda_device, B, H, S, D, caus
     def regular():
         o = torch.empty_like(q)
         lse = torch.empty(B, H, S, dtype=torch.float32, device=dev)
-        # At D <= 64 the regular entry point would pick the separate-P kernel, which needs scratch the
-        # allocation-free call does not have; variant 0 keeps it on the kernel that call runs.
-        assert lib.rsfa_set_option(b"tcgen05_variant", 0 if bn.value == 128 else -1) == _capi.RSFA_OK
-        try:
-            rc = lib.rsfa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, H, S, D,
-                              _strides(q, k, v, o), int(causal), scale, bm.value, bn.value, _capi.RSFA_DTYPE_F16,
-                              stream)
-        finally:
-            lib.rsfa_set_option(b"tcgen05_variant", -1)
+        rc = lib.rsfa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, H, S, D,
+                          _strides(q, k, v, o), int(causal), scale, bm.value, bn.value, _capi.RSFA_DTYPE_F16,
+                          stream)
         assert rc == _capi.RSFA_OK, _capi.strerror(rc)
         return o, lse
 
