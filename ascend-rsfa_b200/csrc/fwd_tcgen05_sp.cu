@@ -23,7 +23,8 @@
 // the scheme): P is taken against a reference fixed at the first key tile, and a check of each
 // tile's row sums says whether a P value may have left the 16-bit range.  Because S_t is gone by
 // the time that check can fail, the fast loop cannot repair a tile.  A work item with a failed
-// check is therefore run a second time by the same CTA, as its next item, with the "safe" loop:
+// check is therefore run a second time by the same CTA, as its next item (only the Q tile whose
+// check failed: the other one's rows are right and written), with the "safe" loop:
 // that one checks each 64-key half while its scores are still in registers and, when a half is
 // over the limit, moves the rows' reference up by a whole number of binary orders and brings l,
 // the tile's first half and O_t along (about a sixth slower per step, so it is not the default).
@@ -51,7 +52,11 @@ constexpr int kMmaWarpSp0 = 9;  // warps 9, 10: one issuer per Q tile
 constexpr int kStagesSp = 6;
 constexpr int kBailOneIn = 4;        // a CTA gives up on the fast loop when more than 1 item in 4 had to be repeated,
 constexpr int kBailMin = 2;          // ... and at least this many were
-constexpr int kSafeItem = 1 << 30;   // flag on a work item number in the scheduler ring: run it with the safe loop
+// A work item in the scheduler ring: its number, a flag "run it with the safe loop", and with that flag the
+// Q tiles to run (bit 28 + t): a repeat only runs the Q tile(s) whose check failed.
+constexpr int kSafeItem = 1 << 30;
+constexpr int kTileBit0 = 28;
+constexpr int kItemMask = (1 << kTileBit0) - 1;
 constexpr int kQBytes = kRows * kD * 2;      // 16 KB
 constexpr int kKvBytes = kKeys * kD * 2;     // 16 KB
 constexpr int kStageBytesSp = kRows * 128;   // epilogue staging per Q tile: 128 rows x 64 columns
@@ -90,8 +95,8 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   const uint32_t bar_sched_full0 = sBar + 8u * (7 * kTiles + 2 * kStagesSp);   // 2 slots
   const uint32_t bar_sched_empty0 = bar_sched_full0 + 16u;                     // 2 slots
   const uint32_t misc = sBar + 8u * kNumBarriersSp;
-  // misc words: [0] TMEM base, [1] abort flag, [2..3] scheduler ring, [4..5] "the item of this ring slot
-  // failed a sum check" (set by its softmax warps before they give the slot back)
+  // misc words: [0] TMEM base, [1] abort flag, [2..3] scheduler ring, [4..5] Q tiles (bit t) of this ring
+  // slot's item that failed a sum check (set by their softmax warps before they give the slot back)
   uint8_t* misc_ptr = smem_raw + (misc - smem_u32(smem_raw));
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(misc_ptr);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc_ptr + 4);
@@ -176,10 +181,11 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           // is its own index: grid <= number of items), fast unless this CTA has given up on that.
           int item = sched.total_items;
           auto take_failed = [&](int sl) {
-            if (item_failed[sl] != 0) {
+            const int tiles = item_failed[sl];
+            if (tiles != 0) {
               item_failed[sl] = 0;
               ++n_failed;
-              item = dispatched[sl] | kSafeItem;
+              item = dispatched[sl] | kSafeItem | (tiles << kTileBit0);
             }
           };
           if (item_count >= 2) take_failed(slot);
@@ -191,7 +197,7 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
               queue_empty = true;
               griddep_launch_dependents();   // the queue is empty: the kernel behind this one may set up
             } else if (n_failed >= kBailMin && n_failed * kBailOneIn > n_fast) {
-              item |= kSafeItem;
+              item |= kSafeItem | (((1 << kTiles) - 1) << kTileBit0);
             } else {
               ++n_fast;
             }
@@ -204,13 +210,13 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
             if (!ok) break;
             take_failed(slot ^ 1);
           }
-          dispatched[slot] = item & ~kSafeItem;
+          dispatched[slot] = item & kItemMask;
           sched_ring[slot] = item;
           __threadfence_block();
           mbar_arrive(bar_sched_full0 + 8u * slot);
           if (item == sched.total_items) break;
           int bh, row0;
-          decode(item & ~kSafeItem, bh, row0);
+          decode(item & kItemMask, bh, row0);
           const int b = bh / p.H, h = bh - b * p.H;
           int nmax = 0;
           for (int t = 0; t < kTiles; ++t) nmax = max(nmax, num_kv_tiles_sp(row0 + t * kRows, S, p.causal));
@@ -263,15 +269,18 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         const int slot = item_count & 1;
         ok = wait_all(bar_sched_full0 + 8u * slot, (item_count >> 1) & 1, kTagSched);
         if (!ok) break;
-        const int item = __shfl_sync(0xffffffffu, sched_ring[slot], 0) & ~kSafeItem;   // fast or safe: the same MMAs
+        const int entry = __shfl_sync(0xffffffffu, sched_ring[slot], 0);
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_sched_empty0 + 8u * slot);
-        if (item >= sched.total_items) break;
+        if (entry == sched.total_items) break;
+        const int item = entry & kItemMask;   // fast or safe: the same MMAs
+        // a repeat may leave this Q tile out: it then only gives its operands back
+        const bool tile_runs = (entry & kSafeItem) == 0 || ((entry >> (kTileBit0 + t)) & 1) != 0;
         int bh, row0;
         decode(item, bh, row0);
         int nmax = 0;
         for (int tt = 0; tt < kTiles; ++tt) nmax = max(nmax, num_kv_tiles_sp(row0 + tt * kRows, S, p.causal));
-        const int n = num_kv_tiles_sp(row0 + t * kRows, S, p.causal);
+        const int n = tile_runs ? num_kv_tiles_sp(row0 + t * kRows, S, p.causal) : 0;
         // S_t = Q_t K^T: both operands K-major in one 64-column box; 16 elements of D per step
         // = 32 B inside the 128-byte swizzle row.
         // MMAs and the commits behind them go out from ONE elected region (an elect.sync and a
@@ -587,13 +596,16 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       const int item = sched_ring[slot];
       if (item == sched.total_items) break;
       ++item_count;
-      const bool failed = (item & kSafeItem) != 0 ? run_item(std::true_type{}, item & ~kSafeItem)
-                                                  : run_item(std::false_type{}, item);
+      bool failed = false;
+      if ((item & kSafeItem) == 0)
+        failed = run_item(std::false_type{}, item);
+      else if (((item >> (kTileBit0 + t)) & 1) != 0)
+        run_item(std::true_type{}, item & kItemMask);
       if (!ok) break;
-      // Done with the item: the ring slot goes back, with the news if it has to be run again.
+      // Done with the item: the ring slot goes back, with the news if this Q tile has to be run again.
       __syncwarp();
       if (lane == 0) {
-        if (failed) item_failed[slot] = 1;
+        if (failed) atomicOr(const_cast<int*>(item_failed) + slot, 1 << t);
         mbar_arrive(bar_sched_empty0 + 8u * slot);
       }
     }
