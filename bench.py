@@ -450,12 +450,18 @@ def main():
             tensors = make_slab(c, 42)
             rec = {"workload": workload_name(name, c, False).replace(" non-causal", "")}
             for causal in (False, True):
-                c_ms, _, tile = timed(c, tensors, causal, 20, 3)
+                # two timed regions of 20 steps, each after its own idle second and warm-up; the faster one is
+                # reported and both are listed (a region now and then starts in a lower power state)
+                regions = []
+                for _ in range(2):
+                    r_ms, _, tile = timed(c, tensors, causal, 20, 3)
+                    regions.append(r_ms)
+                c_ms = min(regions)
                 tf = attention_flops(cB, cH, cS, cD, causal) / (c_ms * 1e-3) / 1e12
                 p_rec, _ = parity(c, tensors, causal, 8 if world == 1 else 2)
                 rec["causal" if causal else "non_causal"] = {
                     "tflops": tf, "ms_per_step": c_ms, "frac_of_measured_burst": tf / world / peaks["burst"],
-                    "tile": list(tile), "steps": 20,
+                    "tile": list(tile), "steps": 20, "ms_per_step_of_each_region": regions,
                     "parity": {"ok": p_rec["ok"], "heads": p_rec["heads"], "ranks": world, "max_abs": p_rec["max_abs"]}}
             configs[name] = rec
             del tensors
