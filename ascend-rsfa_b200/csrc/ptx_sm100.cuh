@@ -75,12 +75,8 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
   return ok != 0;
 }
 
-#ifndef RSFA_WAIT_MODE
-#define RSFA_WAIT_MODE 1   // 0: bare try_wait spin, 1: try_wait with suspend hint, 2: spin + nanosleep back-off
-#endif
-#ifndef RSFA_WAIT_HINT_NS
-#define RSFA_WAIT_HINT_NS 20000
-#endif
+// Longest time the hardware may park a waiting thread per try (it is woken when the phase completes).
+constexpr uint32_t kWaitHintNs = 20000;
 
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by all roles
 // of the CTA: the first role whose wait runs out sets it, every other role sees
@@ -91,17 +87,8 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, vo
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
-#if RSFA_WAIT_MODE == 1
-    if (mbar_try_wait_hint(bar, parity, RSFA_WAIT_HINT_NS)) return true;
-    constexpr uint32_t kCheckMask = 0x3u;
-#else
-    if (mbar_try_wait(bar, parity)) return true;
-    constexpr uint32_t kCheckMask = 0xffu;
-#if RSFA_WAIT_MODE == 2
-    __nanosleep(64);
-#endif
-#endif
-    if ((++spins & kCheckMask) == 0) {
+    if (mbar_try_wait_hint(bar, parity, kWaitHintNs)) return true;
+    if ((++spins & 0x3u) == 0) {   // abort flag and clock every fourth try
       if (*abort_flag != 0) return false;
       if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = (kStatusWaitExpired << 16) | (tag & 0xffff);
