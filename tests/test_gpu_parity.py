@@ -182,6 +182,20 @@ def test_separate_p_kernel_repeats_items_whose_sum_check_failed(fa, cuda_device)
     assert fa.launch_count() - n0 == 3
 
 
+@pytest.mark.parametrize("shape", [(1, 1, 256, 64), (1, 1, 300, 64), (1, 2, 129, 32), (1, 1, 777, 64), (3, 1, 513, 16)])
+def test_separate_p_kernel_repeats_on_the_smallest_grids(fa, cuda_device, shape):
+    # One to nine work items, each on a CTA of its own: the item that fails is the CTA's first and last,
+    # so the repeat is found by the look at the other ring slot that precedes the CTA's exit.
+    B, H, S, D = shape
+    q, k, v = make_inputs(B, H, S, D, seed=S + D)
+    fa.set_option("tcgen05_variant", 2)     # the separate-P kernel also where a single key tile would not take it
+    try:
+        for causal in (False, True):
+            check(fa, q, k, v, causal, 3.0 * (64.0 / D) ** 0.5, 128, 128, cuda_device)
+    finally:
+        fa.set_option("tcgen05_variant", -1)
+
+
 def test_separate_p_kernel_gives_up_on_the_fast_loop_for_one_hot_rows(fa, cuda_device):
     # 512 work items, more than three per CTA: a CTA that has had to repeat more than one item in four
     # runs the rest of its items with the repairing loop at once.  Every item must still come out
