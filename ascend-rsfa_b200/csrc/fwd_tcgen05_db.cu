@@ -157,11 +157,9 @@ fwd_tcgen05_db_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   griddep_wait();
 
   const int S = p.S;
-  const int items_per_head = sched.items_per_head;
   auto decode = [&](int item, int& bh, int& row0) {
-    bh = item / items_per_head;
-    int blk = item - bh * items_per_head;
-    if (p.causal) blk = items_per_head - 1 - blk;   // heaviest block first inside a head
+    int blk;
+    sched_decode(sched, p.causal, item, bh, blk);
     row0 = blk * (NT * kRowsDb);
   };
 
@@ -657,6 +655,7 @@ cudaError_t launch_db(const FwdParams& p, int sm_count, cudaStream_t stream, lon
   if (e != cudaSuccess) return e;
   // No memset of the work queue: the last CTA of the launch that used it before put it back to zero.
   const int grid = sched.total_items < sm_count ? sched.total_items : sm_count;
+  sched_set_tail(sched, p.B * p.H, p.causal, grid);
   e = launch_persistent(kern, grid, C::kThreads, C::kSmemBytes, stream, p.pdl != 0, maps, p, sched);
   if (e == cudaSuccess) *launches += 1;
   return e;

@@ -151,12 +151,10 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
   griddep_wait();
 
   const int S = p.S;
-  const int items_per_head = sched.items_per_head;
   // work item -> (head, first row).  Causal: heaviest (last) row block first.
   auto decode = [&](int item, int& bh, int& row0) {
-    bh = item / items_per_head;
-    int blk = item - bh * items_per_head;
-    if (p.causal) blk = items_per_head - 1 - blk;
+    int blk;
+    sched_decode(sched, p.causal, item, bh, blk);
     row0 = blk * (kTiles * kRows);
   };
 
@@ -646,6 +644,7 @@ static cudaError_t launch_sp_one(const FwdParams& p, int sm_count, cudaStream_t 
   if (e != cudaSuccess) return e;
   // No memset of the work queue: the last CTA of the launch that used it before put it back to zero.
   const int grid = sched.total_items < sm_count ? sched.total_items : sm_count;
+  sched_set_tail(sched, p.B * p.H, p.causal, grid);
   e = launch_persistent(kern, grid, kThreadsSp, kSmemBytesSp, stream, p.pdl != 0, maps, p, sched);
   if (e == cudaSuccess) *launches += 1;
   return e;

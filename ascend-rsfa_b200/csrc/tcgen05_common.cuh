@@ -61,10 +61,44 @@ struct TmaMaps {
   CUtensorMap q, k, v, o;
 };
 
+// Work items = (batch * head, block of Q rows), numbered head-major so that the CTAs working on one head
+// find its K/V in L2; with the causal mask the blocks of a head come heaviest (last rows) first.  The items
+// of the last `tail_heads` heads are numbered differently when the mask makes their sizes differ: block-major
+// (the heaviest block of each of those heads, then the next lighter one of each, ...), so that the queue ends
+// on the lightest items of the launch instead of on a whole head, heaviest block included, and the CTAs
+// finish together.
 struct SchedInfo {
   int total_items;
-  int items_per_head;  // 256-row blocks per head
+  int items_per_head;  // blocks of Q rows per head
+  int tail_first;      // first item of the block-major tail (== total_items: no tail)
+  int tail_heads;
 };
+
+// `sched.total_items` and `sched.items_per_head` set: the tail covers about two items per CTA.
+inline void sched_set_tail(SchedInfo& sched, int heads, int causal, int grid) {
+  sched.tail_first = sched.total_items;
+  sched.tail_heads = 0;
+  if (causal != 0 && sched.items_per_head > 1) {
+    int th = (2 * grid + sched.items_per_head - 1) / sched.items_per_head;
+    if (th > heads) th = heads;
+    sched.tail_heads = th;
+    sched.tail_first = (heads - th) * sched.items_per_head;
+  }
+}
+
+// work item -> (batch * head, block of Q rows)
+__device__ __forceinline__ void sched_decode(const SchedInfo& sched, int causal, int item, int& bh, int& blk) {
+  if (item < sched.tail_first) {
+    bh = item / sched.items_per_head;
+    blk = item - bh * sched.items_per_head;
+    if (causal) blk = sched.items_per_head - 1 - blk;
+  } else {
+    const int r = item - sched.tail_first;
+    const int rank = r / sched.tail_heads;            // 0 = heaviest block
+    bh = sched.tail_first / sched.items_per_head + (r - rank * sched.tail_heads);
+    blk = sched.items_per_head - 1 - rank;
+  }
+}
 
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
