@@ -65,6 +65,8 @@ cudaError_t launch_fwd_tcgen05_db(const FwdParams& p, int sm_count, cudaStream_t
                                   long long* launches);
 // The D = 64 kernel with P in tensor-memory columns of its own (fwd_tcgen05_sp.cu), selected by launch_fwd_tcgen05.
 cudaError_t launch_fwd_tcgen05_sp(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches);
+// Whether a problem's work items can be numbered in that kernel's scheduler ring (fewer than 2^27).
+bool tcgen05_sp_fits(const FwdParams& p);
 // Tile the tcgen05 family runs for a problem: the requested (block_m, block_n) when that tile is
 // instantiated for D, otherwise the tile table's row for (S, D, causal).  `variant` = -1 lets the
 // request / table decide, 0 forces 128-key tiles with single-buffered S, 1 forces 64-key tiles (D <= 128

@@ -736,7 +736,8 @@ cudaError_t launch_fwd_tcgen05(const FwdParams& p, int sm_count, cudaStream_t st
   if (p.D <= 64) {
     // D = 64 (and below): the separate-P kernel, unless single-buffered S is forced.  A single key
     // tile (S <= 128) leaves nothing to overlap: this file's kernel then.
-    if (p.variant != 0 && (p.S > kTileN || p.variant == 2)) return launch_fwd_tcgen05_sp(p, sm_count, stream, launches);
+    if (p.variant != 0 && (p.S > kTileN || p.variant == 2) && tcgen05_sp_fits(p))
+      return launch_fwd_tcgen05_sp(p, sm_count, stream, launches);
     return p.bf16 ? launch_one<64, true>(p, sm_count, stream, launches)
                   : launch_one<64, false>(p, sm_count, stream, launches);
   }

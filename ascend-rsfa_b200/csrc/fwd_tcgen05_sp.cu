@@ -56,7 +56,9 @@ constexpr int kBailMin = 2;          // ... and at least this many were
 // Q tiles to run (bit 28 + t): a repeat only runs the Q tile(s) whose check failed.
 constexpr int kSafeItem = 1 << 30;
 constexpr int kTileBit0 = 28;
-constexpr int kItemMask = (1 << kTileBit0) - 1;
+// ... and a flag "fast loop, but only the Q tiles named": the halves of the items of a last, thin wave
+constexpr int kMaskedItem = 1 << 27;
+constexpr int kItemMask = kMaskedItem - 1;
 constexpr int kQBytes = kRows * kD * 2;      // 16 KB
 constexpr int kKvBytes = kKeys * kD * 2;     // 16 KB
 constexpr int kStageBytesSp = kRows * 128;   // epilogue staging per Q tile: 128 rows x 64 columns
@@ -188,16 +190,26 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
           };
           if (item_count >= 2) take_failed(slot);
           if (item == sched.total_items && !queue_empty) {
-            item = (item_count == 0) ? static_cast<int>(blockIdx.x)
-                                     : static_cast<int>(atomicAdd(p.tile_counter, 1u) + gridDim.x);
-            if (item >= sched.total_items) {
-              item = sched.total_items;
+            // the queue counts whole items first, then two halves for each of the last split_items items
+            const int q = (item_count == 0) ? static_cast<int>(blockIdx.x)
+                                            : static_cast<int>(atomicAdd(p.tile_counter, 1u) + gridDim.x);
+            const int n_whole = sched.total_items - sched.split_items;
+            if (q >= sched.total_items + sched.split_items) {
               queue_empty = true;
               griddep_launch_dependents();   // the queue is empty: the kernel behind this one may set up
-            } else if (n_failed >= kBailMin && n_failed * kBailOneIn > n_fast) {
-              item |= kSafeItem | (((1 << kTiles) - 1) << kTileBit0);
             } else {
-              ++n_fast;
+              int tiles = (1 << kTiles) - 1;
+              item = q;
+              if (q >= n_whole) {
+                item = n_whole + ((q - n_whole) >> 1);
+                tiles = 1 << ((q - n_whole) & 1);
+              }
+              if (n_failed >= kBailMin && n_failed * kBailOneIn > n_fast) {
+                item |= kSafeItem | (tiles << kTileBit0);
+              } else {
+                if (q >= n_whole) item |= kMaskedItem | (tiles << kTileBit0);
+                ++n_fast;
+              }
             }
           }
           if (item == sched.total_items && item_count >= 1) {
@@ -273,7 +285,7 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
         if (entry == sched.total_items) break;
         const int item = entry & kItemMask;   // fast or safe: the same MMAs
         // a repeat may leave this Q tile out: it then only gives its operands back
-        const bool tile_runs = (entry & kSafeItem) == 0 || ((entry >> (kTileBit0 + t)) & 1) != 0;
+        const bool tile_runs = (entry & (kSafeItem | kMaskedItem)) == 0 || ((entry >> (kTileBit0 + t)) & 1) != 0;
         int bh, row0;
         decode(item, bh, row0);
         int nmax = 0;
@@ -595,10 +607,12 @@ fwd_tcgen05_sp_kernel(const __grid_constant__ TmaMaps maps, const FwdParams p, c
       if (item == sched.total_items) break;
       ++item_count;
       bool failed = false;
-      if ((item & kSafeItem) == 0)
-        failed = run_item(std::false_type{}, item);
-      else if (((item >> (kTileBit0 + t)) & 1) != 0)
-        run_item(std::true_type{}, item & kItemMask);
+      if ((item & (kSafeItem | kMaskedItem)) == 0 || ((item >> (kTileBit0 + t)) & 1) != 0) {
+        if ((item & kSafeItem) == 0)
+          failed = run_item(std::false_type{}, item & kItemMask);
+        else
+          run_item(std::true_type{}, item & kItemMask);
+      }
       if (!ok) break;
       // Done with the item: the ring slot goes back, with the news if this Q tile has to be run again.
       __syncwarp();
@@ -638,16 +652,36 @@ static cudaError_t launch_sp_one(const FwdParams& p, int sm_count, cudaStream_t 
   SchedInfo sched;
   sched.items_per_head = (p.S + kTiles * kRows - 1) / (kTiles * kRows);
   sched.total_items = sched.items_per_head * p.B * p.H;
+  if (!tcgen05_sp_fits(p)) return cudaErrorInvalidValue;
   auto kern = fwd_tcgen05_sp_kernel<kBf16>;
   static std::atomic<unsigned long long> smem_done{0};   // per kernel instantiation, bit per device
   cudaError_t e = set_dynamic_smem_once(smem_done, reinterpret_cast<const void*>(kern), kSmemBytesSp);
   if (e != cudaSuccess) return e;
   // No memset of the work queue: the last CTA of the launch that used it before put it back to zero.
-  const int grid = sched.total_items < sm_count ? sched.total_items : sm_count;
+  // Items of equal size (no causal mask) in a last wave that fills at most half the grid, or fewer items
+  // than half the grid altogether, are handed out as single Q tiles: a lone tile takes 0.55 of the time of
+  // the pair, so the launch ends that much sooner.
+  int split = 0;
+  if (!p.causal) {
+    if (2 * sched.total_items <= sm_count) {
+      split = sched.total_items;
+    } else if (sched.total_items > sm_count) {
+      const int r = sched.total_items % sm_count;
+      if (r > 0 && 2 * r <= sm_count) split = r;
+    }
+  }
+  const int n_queue = sched.total_items + split;
+  const int grid = n_queue < sm_count ? n_queue : sm_count;
   sched_set_tail(sched, p.B * p.H, p.causal, grid);
+  sched.split_items = split;
   e = launch_persistent(kern, grid, kThreadsSp, kSmemBytesSp, stream, p.pdl != 0, maps, p, sched);
   if (e == cudaSuccess) *launches += 1;
   return e;
+}
+
+bool tcgen05_sp_fits(const FwdParams& p) {
+  const long long items = static_cast<long long>((p.S + kTiles * kRows - 1) / (kTiles * kRows)) * p.B * p.H;
+  return items < kItemMask;   // the scheduler ring keeps flags in the bits above
 }
 
 cudaError_t launch_fwd_tcgen05_sp(const FwdParams& p, int sm_count, cudaStream_t stream, long long* launches) {

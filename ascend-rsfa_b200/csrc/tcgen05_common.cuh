@@ -72,12 +72,14 @@ struct SchedInfo {
   int items_per_head;  // blocks of Q rows per head
   int tail_first;      // first item of the block-major tail (== total_items: no tail)
   int tail_heads;
+  int split_items;     // separate-P kernel: the last so many items are handed out as two single Q tiles each
 };
 
 // `sched.total_items` and `sched.items_per_head` set: the tail covers about two items per CTA.
 inline void sched_set_tail(SchedInfo& sched, int heads, int causal, int grid) {
   sched.tail_first = sched.total_items;
   sched.tail_heads = 0;
+  sched.split_items = 0;
   if (causal != 0 && sched.items_per_head > 1) {
     int th = (2 * grid + sched.items_per_head - 1) / sched.items_per_head;
     if (th > heads) th = heads;
