@@ -31,10 +31,10 @@
 // A CTA that has had to repeat more than one item in kBailOneIn stops trying the fast loop.
 // Everything is local to the CTA: no list in global memory, no second launch.
 #include <cuda.h>
-
-#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+
+#include <type_traits>
 
 #include "../../include/rsfa.h"
 #include "tcgen05_common.cuh"
